@@ -3,7 +3,7 @@ description as parts.
 
 The reference has a single ``model_type == "qwen3"`` check
 (crates/pagedllm/src/config.rs:89-94) and no registry; this one is keyed on
-``config.json["architectures"][0]`` and falls back to ``model_type``.
+``config.json["architectures"][0]`` and falls back to ``architecture`` and ``model_type``.
 """
 
 from __future__ import annotations
@@ -49,13 +49,14 @@ def resolve_architecture(config_dict: Mapping[str, Any]) -> Architecture:
             tried.append(a)
             if a in _ARCHITECTURES:
                 return _ARCHITECTURES[a]
-    mt = config_dict.get("model_type")
-    if mt is not None:
-        tried.append(mt)
-        if mt in _ARCHITECTURES:
-            return _ARCHITECTURES[mt]
+    for key in ("architecture", "model_type"):      # a single name; `architecture` is how some designs spell it
+        name = config_dict.get(key)
+        if isinstance(name, str):
+            tried.append(name)
+            if name in _ARCHITECTURES:
+                return _ARCHITECTURES[name]
     if not tried:
-        raise ConfigError("config.json names no architecture: neither `architectures` nor `model_type`")
+        raise ConfigError("config.json names no architecture: none of `architectures`, `architecture`, `model_type`")
     raise UnsupportedModelError(
         f"architecture {tried!r} is not registered; known: {architecture_names()}"
     )

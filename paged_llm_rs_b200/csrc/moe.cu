@@ -1,0 +1,249 @@
+// A mixture of gated feed-forward experts: the router, and the experts for a few rows.
+//
+// Router (all float): z = W_r h over every router output (experts with tensors first, identity
+// experts last); s = softmax(z); choice = s + correction.  Outputs form `groups` equal groups of
+// neighbours; a group's score is its largest choice score, and only outputs of the `keep` best groups
+// can be chosen (the others count as minus infinity).  The `top` largest choice scores are chosen; a
+// chosen output's weight is its s divided by the sum of the chosen s (+ 1e-20).  Equal scores go to
+// the lower index.
+//
+// Experts, the weight-streaming form: a (token, chosen expert) pair is a row of its own; a warp
+// forms one output column at a time from that expert's weight rows, so every weight row that a step
+// touches is read once per pair from L2 / HBM and nothing is read for experts that nobody chose.
+//   pair_glu:   act[pair, :] = silu(Wg_e h) * (Wu_e h)
+//   pair_down:  out[t, :] = sum_k w[t, k] * (Wd_e act[pair]  |  h[t] for an identity expert) (+ shared[t, :])
+// The right form for the few tokens of a decode step and for the float32 engine; many rows in bfloat16
+// go to the grouped tensor-core product instead.
+#include "common.cuh"
+
+enum : int { KID_MOE = 60 };
+
+#define MOE_MAX_OUTPUTS 1024
+#define MOE_MAX_TOP 32
+
+// Every lane brings its best (value, index); all leave with the warp's best, ties to the lower index.
+__device__ __forceinline__ void warp_argmax(float& best, int& at) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, at, o);
+        if (ov > best || (ov == best && oi < at)) { best = ov; at = oi; }
+    }
+}
+
+// One warp a token.  h in T (the float32 engine's h is float); router weights and correction float.
+template <typename T>
+__global__ void __launch_bounds__(128) moe_route_kernel(const T* h, const float* __restrict__ w_router,
+                                                        const float* __restrict__ correction, int* __restrict__ ids,
+                                                        float* __restrict__ weights, int n_tokens, int width, int outputs,
+                                                        int top, int groups, int keep) {
+    extern __shared__ float smem[];      // per warp: s[outputs], choice[outputs], gscore[groups]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    float* s = smem + (size_t)warp * (2 * outputs + groups);
+    float* choice = s + outputs;
+    float* gscore = choice + outputs;
+    pdl_launch_dependents();
+    pdl_wait(KID_MOE);
+    if (t >= n_tokens) return;
+    const T* hr = h + (size_t)t * width;
+    float zmax = -CUDART_INF_F;
+    for (int e = 0; e < outputs; e++) {
+        const float* wr = w_router + (size_t)e * width;
+        float acc = 0.f;
+        for (int c = lane; c < width; c += 32) acc = fmaf(to_f32(hr[c]), wr[c], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) s[e] = acc;
+        zmax = fmaxf(zmax, acc);
+    }
+    __syncwarp();
+    float sum = 0.f;
+    for (int e = lane; e < outputs; e += 32) { const float p = expf(s[e] - zmax); s[e] = p; sum += p; }
+    sum = warp_sum(sum);
+    __syncwarp();
+    for (int e = lane; e < outputs; e += 32) {
+        const float p = s[e] / sum;
+        s[e] = p;
+        choice[e] = p + (correction ? correction[e] : 0.f);
+    }
+    __syncwarp();
+    // groups: keep the best `keep`, the others' outputs cannot be chosen
+    if (groups > 1 && keep < groups) {
+        const int per = outputs / groups;
+        for (int g = lane; g < groups; g += 32) {
+            float gs = -CUDART_INF_F;
+            for (int j = 0; j < per; j++) gs = fmaxf(gs, choice[g * per + j]);
+            gscore[g] = gs;
+        }
+        __syncwarp();
+        for (int round = 0; round < keep; round++) {
+            float best = -CUDART_INF_F; int at = 0x7fffffff;
+            for (int g = lane; g < groups; g += 32) {
+                const float gs = gscore[g];                    // (a kept group holds NaN and compares false)
+                if (gs > best || (gs == best && g < at)) { best = gs; at = g; }
+            }
+            warp_argmax(best, at);
+            __syncwarp();
+            if (lane == 0 && at != 0x7fffffff) gscore[at] = CUDART_NAN_F;
+            __syncwarp();
+        }
+        for (int e = lane; e < outputs; e += 32)
+            if (!isnan(gscore[e / per])) choice[e] = -CUDART_INF_F;
+        __syncwarp();
+    }
+    // the `top` best choice scores
+    float wsum = 0.f;
+    int mine_id = 0; float mine_s = 0.f;      // lane k holds the k-th choice (top <= 32)
+    for (int k = 0; k < top; k++) {
+        float best = -CUDART_INF_F; int at = 0x7fffffff;
+        for (int e = lane; e < outputs; e += 32) {
+            const float c = choice[e];
+            if (c > best || (c == best && e < at && c > -CUDART_INF_F)) { best = c; at = e; }
+        }
+        warp_argmax(best, at);
+        if (at == 0x7fffffff) at = 0;          // (cannot happen for a valid configuration)
+        const float p = s[at];
+        wsum += p;
+        if (lane == k) { mine_id = at; mine_s = p; }
+        __syncwarp();
+        if (lane == 0) choice[at] = -CUDART_INF_F;
+        __syncwarp();
+    }
+    if (lane < top) {
+        ids[(size_t)t * top + lane] = mine_id;
+        weights[(size_t)t * top + lane] = mine_s / (wsum + 1e-20f);
+    }
+}
+
+PLLM_EXPORT int pllm_moe_route(int dtype, const void* h, const float* w_router, const float* correction, int* ids, float* weights,
+                               int n_tokens, int width, int outputs, int top, int groups, int keep, cudaStream_t stream) {
+    if (n_tokens <= 0) return PLLM_OK;
+    if (width <= 0 || outputs <= 0 || top <= 0 || groups <= 0 || keep <= 0 || outputs % groups || keep > groups) return PLLM_ERR_SIZE;
+    if (outputs > MOE_MAX_OUTPUTS || top > MOE_MAX_TOP || top > outputs) return PLLM_ERR_LIMIT;
+    PLLM_DISPATCH_DTYPE(dtype, {
+        const int warps = 4;
+        launch_chained(moe_route_kernel<T>, dim3((n_tokens + warps - 1) / warps), dim3(warps * 32),
+                       (size_t)warps * (2 * outputs + groups) * sizeof(float), stream, (const T*)h, w_router, correction, ids, weights,
+                       n_tokens, width, outputs, top, groups, keep);
+    });
+    return launch_status();
+}
+
+// ---- the experts for a few rows -----------------------------------------------------------------
+// w_gu: [experts, 2 * ff, width] (an expert's gate rows, then its up rows); act: [pairs, ff].
+// grid (pairs, column blocks); a CTA keeps the token's row in shared memory as floats.
+template <typename T>
+__global__ void __launch_bounds__(256) moe_pair_glu_kernel(const T* h, const int* ids, const T* __restrict__ w_gu, T* __restrict__ act,
+                                                           int width, int ff, int top, int experts, int cols_per_cta) {
+    extern __shared__ float xs[];
+    const int pair = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    pdl_launch_dependents();
+    pdl_wait(KID_MOE);
+    const int e = ids[pair];
+    if (e < 0 || e >= experts) return;             // an identity expert has no product
+    const T* hr = h + (size_t)(pair / top) * width;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) xs[c] = to_f32(hr[c]);
+    __syncthreads();
+    const T* wg = w_gu + (size_t)e * 2 * ff * width;
+    const T* wu = wg + (size_t)ff * width;
+    const int col0 = blockIdx.y * cols_per_cta;
+    const int col1 = min(ff, col0 + cols_per_cta);
+    constexpr int N = Vec16<T>::N;
+    const bool vec = width % N == 0;
+    for (int col = col0 + warp; col < col1; col += warps) {
+        const T* g = wg + (size_t)col * width;
+        const T* u = wu + (size_t)col * width;
+        float ag = 0.f, au = 0.f;
+        if (vec) {
+            for (int c = lane * N; c < width; c += 32 * N) {
+                Vec16<T> vg, vu; vg.load(g + c); vu.load(u + c);
+                float fg[N], fu[N]; vg.unpack(fg); vu.unpack(fu);
+#pragma unroll
+                for (int k = 0; k < N; k++) { ag = fmaf(xs[c + k], fg[k], ag); au = fmaf(xs[c + k], fu[k], au); }
+            }
+        } else {
+            for (int c = lane; c < width; c += 32) { ag = fmaf(xs[c], to_f32(g[c]), ag); au = fmaf(xs[c], to_f32(u[c]), au); }
+        }
+        ag = warp_sum(ag); au = warp_sum(au);
+        if (lane == 0) act[(size_t)pair * ff + col] = from_f32<T>(ag / (1.0f + expf(-ag)) * au);
+    }
+}
+
+// w_d: [experts, width, ff].  grid (tokens, column blocks).  shared: [tokens, width] or null.
+template <typename T>
+__global__ void __launch_bounds__(256) moe_pair_down_kernel(const T* act, const T* h, const int* ids, const float* weights,
+                                                            const T* __restrict__ w_d, const T* shared, T* __restrict__ out,
+                                                            int width, int ff, int top, int experts, int cols_per_cta) {
+    extern __shared__ float xs[];                 // [top][ff] the token's activations, as floats
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    pdl_launch_dependents();
+    pdl_wait(KID_MOE);
+    for (int k = 0; k < top; k++) {
+        const int e = ids[(size_t)t * top + k];
+        if (e < 0 || e >= experts) continue;
+        const T* ar = act + ((size_t)t * top + k) * ff;
+        for (int c = threadIdx.x; c < ff; c += blockDim.x) xs[k * ff + c] = to_f32(ar[c]);
+    }
+    __syncthreads();
+    const int col0 = blockIdx.y * cols_per_cta;
+    const int col1 = min(width, col0 + cols_per_cta);
+    constexpr int N = Vec16<T>::N;
+    const bool vec = ff % N == 0;
+    for (int col = col0 + warp; col < col1; col += warps) {
+        float total = 0.f;
+        for (int k = 0; k < top; k++) {
+            const int e = ids[(size_t)t * top + k];
+            const float wk = weights[(size_t)t * top + k];
+            if (e < 0 || e >= experts) {           // identity: the input itself
+                total += wk * to_f32(h[(size_t)t * width + col]);
+                continue;
+            }
+            const T* d = w_d + ((size_t)e * width + col) * ff;
+            const float* x = xs + k * ff;
+            float acc = 0.f;
+            if (vec) {
+                for (int c = lane * N; c < ff; c += 32 * N) {
+                    Vec16<T> vd; vd.load(d + c);
+                    float fd[N]; vd.unpack(fd);
+#pragma unroll
+                    for (int j = 0; j < N; j++) acc = fmaf(x[c + j], fd[j], acc);
+                }
+            } else {
+                for (int c = lane; c < ff; c += 32) acc = fmaf(x[c], to_f32(d[c]), acc);
+            }
+            total += wk * warp_sum(acc);
+        }
+        if (shared) total += to_f32(shared[(size_t)t * width + col]);
+        if (lane == 0) out[(size_t)t * width + col] = from_f32<T>(total);
+    }
+}
+
+PLLM_EXPORT int pllm_moe_pair_glu(int dtype, const void* h, const int* ids, const void* w_gu, void* act, int n_tokens, int width,
+                                  int ff, int top, int experts, cudaStream_t stream) {
+    if (n_tokens <= 0) return PLLM_OK;
+    if (width <= 0 || ff <= 0 || top <= 0 || experts <= 0) return PLLM_ERR_SIZE;
+    if ((size_t)width * sizeof(float) > 48 * 1024) return PLLM_ERR_LIMIT;
+    PLLM_DISPATCH_DTYPE(dtype, {
+        const int cols = 64;
+        launch_chained(moe_pair_glu_kernel<T>, dim3(n_tokens * top, (ff + cols - 1) / cols), dim3(256), (size_t)width * sizeof(float),
+                       stream, (const T*)h, ids, (const T*)w_gu, (T*)act, width, ff, top, experts, cols);
+    });
+    return launch_status();
+}
+
+PLLM_EXPORT int pllm_moe_pair_down(int dtype, const void* act, const void* h, const int* ids, const float* weights, const void* w_d,
+                                   const void* shared, void* out, int n_tokens, int width, int ff, int top, int experts,
+                                   cudaStream_t stream) {
+    if (n_tokens <= 0) return PLLM_OK;
+    if (width <= 0 || ff <= 0 || top <= 0 || experts <= 0) return PLLM_ERR_SIZE;
+    if ((size_t)top * ff * sizeof(float) > 48 * 1024) return PLLM_ERR_LIMIT;
+    PLLM_DISPATCH_DTYPE(dtype, {
+        const int cols = 64;
+        launch_chained(moe_pair_down_kernel<T>, dim3(n_tokens, (width + cols - 1) / cols), dim3(256),
+                       (size_t)top * ff * sizeof(float), stream, (const T*)act, (const T*)h, ids, weights, (const T*)w_d,
+                       (const T*)shared, (T*)out, width, ff, top, experts, cols);
+    });
+    return launch_status();
+}
+
+PLLM_TRACE_EXPORT(moe)

@@ -67,6 +67,18 @@ def lib():
         sig["pllm_attention_prefill_tcgen05"] = [P] * 10 + [c_int] * 7 + [c_float, c_int, P, P]
         sig["pllm_gemm_tcgen05_supports"] = [c_int, c_int, c_int, c_int]
         sig["pllm_gemm_tcgen05"] = [P, P, P, c_int, c_int, c_int, c_int, P, P]
+        sig["pllm_embed_scaled32"] = [c_int, P, P, P, c_int, c_int, c_int, c_float, P, P]
+        sig["pllm_sinusoid_add"] = [P, P, P, c_int, c_int, P]
+        sig["pllm_round_rows"] = [c_int, P, P, c_ll, P]
+        sig["pllm_outnorm_add"] = [c_int, P, P, P, P, c_int, c_int, c_float, P]
+        sig["pllm_rmsnorm_from32"] = [c_int, P, P, P, P, c_int, c_int, c_float, P]
+        sig["pllm_latent_norm_write"] = [c_int, P, P, P, c_float, P, P, P, c_int, c_int, c_int, c_ll, P, P]
+        sig["pllm_latent_attention_generic_tile_tokens"] = [c_int]
+        sig["pllm_latent_attention_generic_ctas_per_item"] = [c_int]
+        sig["pllm_latent_attention_generic"] = [c_int, P, P, P, P, P, c_int, P, P, P] + [c_int] * 5 + [c_float, P, P]
+        sig["pllm_moe_route"] = [c_int, P, P, P, P, P] + [c_int] * 6 + [P]
+        sig["pllm_moe_pair_glu"] = [c_int, P, P, P, P] + [c_int] * 5 + [P]
+        sig["pllm_moe_pair_down"] = [c_int, P, P, P, P, P, P, P] + [c_int] * 5 + [P]
         sig["pllm_pack_decode_step"] = [P, c_int, c_int, P, P, P, P, P] + [c_int] * 16 + [P, P]
         for name, args in sig.items():
             fn = getattr(L, name)
@@ -592,3 +604,175 @@ def linear_glu(x: torch.Tensor, w_gate_up: torch.Tensor, status: Optional[torch.
     gu = linear(x, w_gate_up)
     act = torch.empty((gu.shape[0], inter), dtype=gu.dtype, device=gu.device)
     return swiglu(gu, act)
+
+
+# ---- a residual stream kept in float32 (csrc/stream32.cu) ---------------------------------------------
+
+def _code_of(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return _F32
+    if dtype == torch.bfloat16:
+        return _BF16
+    raise KernelError(f"dtype {dtype} is not handled: the kernels take float32 and bfloat16")
+
+
+def embed_scaled32(tokens: torch.Tensor, table: torch.Tensor, scale: float, out: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
+    """out[t] = table[tokens[t]] * scale as float32, whatever the table's dtype."""
+    _dev(tokens, table, out, status)
+    _i32(tokens, "tokens"); _f32(out, "out")
+    T, (V, H) = tokens.numel(), table.shape
+    if out.shape != (T, H):
+        raise KernelError(f"embed_scaled32: out is {tuple(out.shape)}, expected {(T, H)}")
+    _check(lib().pllm_embed_scaled32(_code(table), _ptr(tokens), _ptr(table), _ptr(out), T, H, V, float(scale), _ptr(status),
+                                     _stream()), "embed_scaled32")
+    return out
+
+
+def sinusoid_add(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    """x[t, 2i] += sin(p_t f_i), x[t, 2i + 1] += cos(p_t f_i) in place; x float32 [T, width], inv_freq float32 [width / 2]."""
+    _dev(x, positions, inv_freq)
+    _f32(x, "x"); _f32(inv_freq, "inv_freq"); _i32(positions, "positions")
+    T, W = x.shape
+    if inv_freq.numel() * 2 != W or positions.numel() < T:
+        raise KernelError("sinusoid_add: inv_freq must hold width / 2 entries and positions one per row")
+    _check(lib().pllm_sinusoid_add(_ptr(x), _ptr(positions), _ptr(inv_freq), T, W, _stream()), "sinusoid_add")
+    return x
+
+
+def round_rows(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """A copy of the float32 tensor x rounded to ``dtype``."""
+    _dev(x)
+    _f32(x, "x")
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    _check(lib().pllm_round_rows(_code_of(dtype), _ptr(x), _ptr(out), x.numel(), _stream()), "round_rows")
+    return out
+
+
+def outnorm_add(x: torch.Tensor, a: torch.Tensor, gain: torch.Tensor, eps: float, h: Optional[torch.Tensor]) -> torch.Tensor:
+    """x += a / sqrt(mean(a^2) + eps) * gain, row by row, x float32 in place; h (a's dtype, or None) receives x rounded."""
+    _dev(x, a, gain, h)
+    _f32(x, "x"); _f32(gain, "gain")
+    n, W = x.shape
+    if a.shape != x.shape or gain.numel() != W or (h is not None and (h.shape != x.shape or h.dtype != a.dtype)):
+        raise KernelError("outnorm_add: a and h must have x's shape, gain its width")
+    _check(lib().pllm_outnorm_add(_code(a), _ptr(x), _ptr(a), _ptr(gain), _ptr(h), n, W, float(eps), _stream()), "outnorm_add")
+    return x
+
+
+def rmsnorm_from32(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[i] = rmsnorm(x[r]) * gain for float32 x, r = rows[i] or i; out in float32 or bfloat16."""
+    _dev(x, gain, out, rows)
+    _f32(x, "x"); _f32(gain, "gain"); _i32(rows, "rows")
+    W = x.shape[-1]
+    n = rows.numel() if rows is not None else x.shape[0]
+    if gain.numel() != W or out.shape != (n, W):
+        raise KernelError("rmsnorm_from32: out or gain does not fit")
+    _check(lib().pllm_rmsnorm_from32(_code(out), _ptr(x), _ptr(gain), _ptr(out), _ptr(rows), n, W, float(eps), _stream()),
+           "rmsnorm_from32")
+    return out
+
+
+# ---- latent attention (csrc/latent.cu) --------------------------------------------------------------------
+
+def latent_norm_write(qa: torch.Tensor, q_gain: torch.Tensor, kv_gain: torch.Tensor, eps: float, cq: torch.Tensor,
+                      pool: Optional[torch.Tensor], slots: Optional[torch.Tensor], q_rank: int, kv_rank: int,
+                      status: torch.Tensor) -> torch.Tensor:
+    """qa [T, q_rank + kv_rank]: RMS norm of both parts; the first to cq [T, q_rank], the second to row ``slots[t]`` of
+    the paged pool [pages, page_size, kv_rank] (a negative slot, or pool None, writes nothing)."""
+    _dev(qa, q_gain, kv_gain, cq, pool, slots, status)
+    _f32(q_gain, "q_gain"); _f32(kv_gain, "kv_gain"); _i32(slots, "slots")
+    T = qa.shape[0]
+    if qa.shape != (T, q_rank + kv_rank) or cq.shape != (T, q_rank) or cq.dtype != qa.dtype:
+        raise KernelError("latent_norm_write: qa must be [T, q_rank + kv_rank] and cq [T, q_rank] of one dtype")
+    if q_gain.numel() != q_rank or kv_gain.numel() != kv_rank:
+        raise KernelError("latent_norm_write: a gain does not fit its latent")
+    rows = 0
+    if pool is not None:
+        if pool.dtype != qa.dtype or pool.shape[-1] != kv_rank or slots is None or slots.numel() < T:
+            raise KernelError("latent_norm_write: the pool must hold rows of kv_rank values of qa's dtype, with a slot a token")
+        rows = pool.numel() // kv_rank
+    _check(lib().pllm_latent_norm_write(_code(qa), _ptr(qa), _ptr(q_gain), _ptr(kv_gain), float(eps), _ptr(cq), _ptr(pool),
+                                        _ptr(slots), T, q_rank, kv_rank, rows, _ptr(status), _stream()), "latent_norm_write")
+    return cq
+
+
+def latent_attention_tile_tokens(heads: int, kv_rank: int, dtype: torch.dtype) -> int:
+    """The most query tokens one work item of ``latent_attention`` may hold."""
+    return int(lib().pllm_latent_attention_generic_tile_tokens(int(heads)))
+
+
+def latent_attention_ctas_per_item(heads: int, kv_rank: int, dtype: torch.dtype) -> int:
+    return int(lib().pllm_latent_attention_generic_ctas_per_item(int(heads)))
+
+
+def latent_attention(q: torch.Tensor, rows: torch.Tensor, block_tables: torch.Tensor, w, out: torch.Tensor, scale: float,
+                     status: torch.Tensor) -> torch.Tensor:
+    """Attention of every head over one shared row a cached token, the rows being keys and values at once:
+    q, out [tokens, heads, R]; rows the paged pool [pages, page_size, R]; ``w`` the group's ``AttentionWork``.
+    Then the reduction of split items."""
+    work, n_work, max_work, red, n_red, max_red = w.work, w.n_work, w.max_work, w.red, w.n_red, w.max_red
+    part_o, part_ml = w.part_o, w.part_ml
+    _dev(q, rows, block_tables, work, n_work, out, part_o, part_ml, red, n_red, status)
+    for t, n in ((block_tables, "block_tables"), (work, "work"), (n_work, "n_work"), (red, "red"), (n_red, "n_red")):
+        _i32(t, n)
+    _f32(part_o, "part_o"); _f32(part_ml, "part_ml")
+    T, H, R = q.shape
+    if rows.dim() != 3 or rows.shape[2] != R or rows.dtype != q.dtype or out.shape != q.shape or out.dtype != q.dtype:
+        raise KernelError("latent_attention: q and out must be [tokens, heads, R], the pool [pages, page_size, R], of one dtype")
+    if part_o.shape[1:] != (H, R) or part_ml.shape[1:] != (H, 2):
+        raise KernelError("latent_attention: the scratch for partial results is not [rows, heads, R] and [rows, heads, 2]")
+    if work.numel() < max_work * 8 or red.numel() < max_red * 4:
+        raise KernelError("latent_attention: work / red lists shorter than their maxima")
+    n_pages, page_size = rows.shape[0], rows.shape[1]
+    L = lib()
+    _check(L.pllm_latent_attention_generic(_code(q), _ptr(q), _ptr(rows), _ptr(block_tables), _ptr(work), _ptr(n_work), max_work,
+                                           _ptr(out), _ptr(part_o), _ptr(part_ml), H, R, page_size, n_pages,
+                                           block_tables.shape[-1], float(scale), _ptr(status), _stream()), "latent_attention")
+    _check(L.pllm_attention_reduce(_code(q), _ptr(part_o), _ptr(part_ml), _ptr(red), _ptr(n_red), max_red, _ptr(out), H, R,
+                                   1 if (w.many_splits and R * 4 <= 1024) else 0, _stream()), "attention_reduce")
+    return out
+
+
+# ---- mixture of experts (csrc/moe.cu) -----------------------------------------------------------------------
+
+def moe_route(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], top: int, groups: int, keep: int):
+    """The router: (ids int32 [T, top], weights float32 [T, top]).  w_router float32 [outputs, width]."""
+    _dev(h, w_router, correction)
+    _f32(w_router, "w_router"); _f32(correction, "correction")
+    T, W = h.shape
+    E = w_router.shape[0]
+    if w_router.shape[1] != W or (correction is not None and correction.numel() != E):
+        raise KernelError("moe_route: the router's weight or correction does not fit")
+    ids = torch.empty((T, top), dtype=torch.int32, device=h.device)
+    weights = torch.empty((T, top), dtype=torch.float32, device=h.device)
+    _check(lib().pllm_moe_route(_code(h), _ptr(h), _ptr(w_router), _ptr(correction), _ptr(ids), _ptr(weights), T, W, E,
+                                int(top), int(groups), int(keep), _stream()), "moe_route")
+    return ids, weights
+
+
+def moe_experts_few(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gu: torch.Tensor, w_d: torch.Tensor,
+                    shared: Optional[torch.Tensor]) -> torch.Tensor:
+    """sum_k weights[t, k] * expert_{ids[t, k]}(h[t]) (+ shared[t]); an id at or above the experts with tensors is the
+    identity.  w_gu [experts, 2 ff, width] (gate rows, then up rows), w_d [experts, width, ff].  The weight-streaming form."""
+    _dev(h, ids, weights, w_gu, w_d, shared)
+    _i32(ids, "ids"); _f32(weights, "weights")
+    T, W = h.shape
+    E, two_ff, _ = w_gu.shape
+    ff, top = two_ff // 2, ids.shape[1]
+    if w_gu.shape != (E, 2 * ff, W) or w_d.shape != (E, W, ff) or w_gu.dtype != h.dtype or w_d.dtype != h.dtype:
+        raise KernelError("moe_experts_few: expert weights do not fit")
+    if shared is not None and (shared.shape != h.shape or shared.dtype != h.dtype):
+        raise KernelError("moe_experts_few: the shared expert's output must have h's shape and dtype")
+    act = torch.empty((T * top, ff), dtype=h.dtype, device=h.device)
+    out = torch.empty_like(h)
+    L = lib()
+    _check(L.pllm_moe_pair_glu(_code(h), _ptr(h), _ptr(ids), _ptr(w_gu), _ptr(act), T, W, ff, top, E, _stream()), "moe_pair_glu")
+    _check(L.pllm_moe_pair_down(_code(h), _ptr(act), _ptr(h), _ptr(ids), _ptr(weights), _ptr(w_d), _ptr(shared), _ptr(out),
+                                T, W, ff, top, E, _stream()), "moe_pair_down")
+    return out
+
+
+def moe_experts(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gu: torch.Tensor, w_d: torch.Tensor,
+                shared: Optional[torch.Tensor]) -> torch.Tensor:
+    """The routed experts' weighted sum (+ the shared expert's output), by the form that fits the step."""
+    return moe_experts_few(h, ids, weights, w_gu, w_d, shared)

@@ -1,1 +1,2 @@
 from . import qwen3  # registers Qwen3ForCausalLM
+from . import surelorn  # registers Surelorn

@@ -286,6 +286,12 @@ class Block:
     def forward(self, residual, delta, step: StepState, cache, writes_cache: bool):
         raise NotImplementedError
 
+    def settle(self, residual, handed_on):
+        """Called on the last block's pair before the model's final norm: returns (residual, pending
+        addition or None).  An arrangement that hands on something other than a pending addition
+        drops or applies it here."""
+        return residual, handed_on
+
     # An arrangement may also give its forward in two halves around the mixer:
     #   h = pre_mixer(residual, delta);  a = mixer.forward(h, step, cache, writes_cache);
     #   residual, delta = post_mixer(residual, a, step)

@@ -5,6 +5,9 @@ addition that is still pending."""
 
 from __future__ import annotations
 
+import torch
+
+from ..kernels import ops
 from .base import Block, register_block
 
 
@@ -26,4 +29,29 @@ class PreNormResidualBlock(Block):
         return self.post_mixer(residual, a, step)
 
 
+class OutputNormResidualBlock(Block):
+    """x + norm(mixer(x)), then x + norm(ff(x)): the norm sits on each sublayer's output and the
+    sublayers read the stream itself.  The stream is float32 and is added to in place; what is
+    handed on beside it is its rounding to the compute dtype (None before the first block, the
+    stream itself in a float32 engine), not a pending addition.  A layer may have no feed-forward.
+    Its norms are ``StreamRMSNorm``s."""
+
+    def forward(self, stream, rounded, step, cache, writes_cache=True):
+        rt = self.mixer.rt
+        if rounded is None:
+            rounded = stream if rt.dtype == torch.float32 else ops.round_rows(stream, rt.dtype)
+        a = self.mixer.forward(rounded, step, cache, writes_cache)
+        rounded = self.norms["mixer"].add_into(stream, a)
+        if self.feed_forward is not None:
+            f = self.feed_forward.forward(rounded, step)
+            rounded = self.norms["feed_forward"].add_into(stream, f)
+        if rt.trace is not None and self.prefix:
+            rt.record(f"{self.prefix}.out", stream)
+        return stream, rounded
+
+    def settle(self, stream, rounded):
+        return stream, None
+
+
 register_block("prenorm_residual", PreNormResidualBlock)
+register_block("outnorm_residual", OutputNormResidualBlock)

@@ -12,7 +12,8 @@ from typing import Dict, List, Optional
 
 import torch
 
-from . import attention, block, embedding, feed_forward, norm, position  # noqa: F401  (register the parts)
+from . import (attention, block, embedding, feed_forward, latent_attention, norm, position,  # noqa: F401  (register the parts)
+               routed_feed_forward)
 from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, Runtime, StepState,
                    make)
 from .spec import ModelSpec, TensorSpec
@@ -28,7 +29,7 @@ class DecoderModel:
         self.blocks = []
         for ls in spec.layers:
             mixer = make(MIXERS, "mixer", ls.mixer, rt, position_encodings=self.position_encodings)
-            ff = make(FEED_FORWARDS, "feed-forward", ls.feed_forward, rt)
+            ff = make(FEED_FORWARDS, "feed-forward", ls.feed_forward, rt) if ls.feed_forward is not None else None
             norms = {k: make(NORMS, "norm", ns, rt) for k, ns in ls.norms.items()}
             if ls.block not in BLOCKS:
                 raise KeyError(f"no block arrangement {ls.block!r} is registered; known: {sorted(BLOCKS)}")
@@ -43,7 +44,8 @@ class DecoderModel:
         yield self.embedding
         for b in self.blocks:
             yield b.mixer
-            yield b.feed_forward
+            if b.feed_forward is not None:
+                yield b.feed_forward
             yield from b.norms.values()
         yield self.final_norm
         yield self.head
@@ -85,6 +87,8 @@ class DecoderModel:
                 residual, delta = blk.post_mixer(residual, a, step)
                 continue
             residual, delta = blk.forward(residual, delta, step, cache, own)
+        if self.schedule:
+            residual, delta = self.blocks[self.schedule[-1].layer].settle(residual, delta)
         if step.n_wanted == 0:
             # A portion in the middle of a prompt runs only to fill the cache (mod.rs:336-346).
             return torch.zeros((0, self.spec.vocab_size), dtype=torch.float32, device=self.rt.device)

@@ -1,5 +1,7 @@
 """Token embedding (crates/pagedllm/src/model/mod.rs:323-327: a row gather, no
-scale) and the output head (mod.rs:222-236, 350-351: ``lm_head.weight`` when the
+scale; with ``scale`` the rows are multiplied by it, and with ``stream="float32"`` they
+leave as float32 whatever the table's dtype, for a decoder that keeps its residual sum
+unrounded) and the output head (mod.rs:222-236, 350-351: ``lm_head.weight`` when the
 file has it, else the embedding when the config ties them, else an error).
 Logits leave the head in float32."""
 
@@ -17,15 +19,28 @@ class TokenEmbedding(Part):
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
         self.vocab, self.hidden = int(spec.params["vocab_size"]), int(spec.params["hidden_size"])
+        self.scale = float(spec.params.get("scale", 1.0))
+        self.stream32 = spec.params.get("stream") == "float32"
+        self.leaf = spec.params.get("leaf", "weight")      # the table's name under the prefix ("" when the prefix is the name)
+        if self.scale != 1.0 and not self.stream32:
+            raise ValueError("a scaled embedding leaves as float32: give stream='float32'")
         self.table = None
 
+    def _table_name(self):
+        return self._name(self.leaf) if self.leaf else self.prefix
+
     def tensors(self):
-        return [TensorSpec(self._name("weight"), (self.vocab, self.hidden))]
+        return [TensorSpec(self._table_name(), (self.vocab, self.hidden))]
 
     def bind(self, tensors):
-        self.table = tensors[self._name("weight")]
+        self.table = tensors[self._table_name()]
 
     def forward(self, tokens: torch.Tensor) -> torch.Tensor:
+        if self.stream32:
+            out = torch.empty((tokens.numel(), self.hidden), dtype=torch.float32, device=self.table.device)
+            ops.embed_scaled32(tokens, self.table, self.scale, out, self.rt.status)
+            self.rt.record(self._name("out"), out)
+            return out
         out = torch.empty((tokens.numel(), self.hidden), dtype=self.table.dtype, device=self.table.device)
         ops.embed(tokens, self.table, out, self.rt.status)
         self.rt.record(self._name("out"), out)
@@ -38,7 +53,13 @@ class LinearHead(Part):
         p = spec.params
         self.vocab, self.hidden = int(p["vocab_size"]), int(p["hidden_size"])
         self.tied, self.tied_to = bool(p.get("tied", False)), p.get("tied_to")
+        self.leaf = p.get("leaf", "weight")
         self.weight = None
+
+    def _name(self, leaf: str) -> str:
+        if leaf == "weight":
+            return super()._name(self.leaf) if self.leaf else self.prefix
+        return super()._name(leaf)
 
     def tensors(self):
         t = [TensorSpec(self._name("weight"), (self.vocab, self.hidden), optional=self.tied)]

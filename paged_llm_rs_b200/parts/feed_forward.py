@@ -17,16 +17,21 @@ class SwiGLUMLP(FeedForward):
         super().__init__(spec, rt)
         self.hidden = int(spec.params["hidden_size"])
         self.inter = int(spec.params["intermediate_size"])
+        # the three tensors' leaves under the prefix (another checkpoint layout names them otherwise)
+        self.names = dict(gate="gate_proj.weight", up="up_proj.weight", down="down_proj.weight")
+        self.names.update(spec.params.get("names", {}))
         self.w_gate_up = self.w_down = None
 
     def tensors(self):
-        return [TensorSpec(self._name("gate_proj.weight"), (self.inter, self.hidden)),
-                TensorSpec(self._name("up_proj.weight"), (self.inter, self.hidden)),
-                TensorSpec(self._name("down_proj.weight"), (self.hidden, self.inter))]
+        n = self.names
+        return [TensorSpec(self._name(n["gate"]), (self.inter, self.hidden)),
+                TensorSpec(self._name(n["up"]), (self.inter, self.hidden)),
+                TensorSpec(self._name(n["down"]), (self.hidden, self.inter))]
 
     def bind(self, tensors):
-        self.w_gate_up = torch.cat([tensors[self._name("gate_proj.weight")], tensors[self._name("up_proj.weight")]], 0)
-        self.w_down = tensors[self._name("down_proj.weight")]
+        n = self.names
+        self.w_gate_up = torch.cat([tensors[self._name(n["gate"])], tensors[self._name(n["up"])]], 0)
+        self.w_down = tensors[self._name(n["down"])]
 
     def forward(self, x, step):
         act = ops.linear_glu(x, self.w_gate_up, status=self.rt.status)

@@ -1,0 +1,101 @@
+"""Latent attention: keys and values of every head are linear in ONE cached row a token.
+
+With h the mixer's input, per token
+
+    c_q = norm(W_dq h) g_q          q_a = W_uq c_q  (head a: ``dim`` values)
+    c   = norm(W_dkv h) g_kv        k_a = W_uk,a c     v_a = W_uv,a c
+    score(i, j, a) = scale * q_a(i) . k_a(j),   causal softmax over j <= i,   out = W_o [sum_j p v_a(j)]_a
+
+Only c (``kv_rank`` values a token) is kept between steps, as rows of a paged pool (``RowNeed``).
+The products with W_uk and W_uv are moved across the sum over cached tokens, which changes no
+value beyond rounding:
+
+    q~_a(i) = W_uk,a^T q_a(i)              (kv_rank values a head)
+    score   = scale * q~_a(i) . c(j)
+    o~_a(i) = sum_j p(i, j, a) c(j)        (kv_rank values a head)
+    out     = W_o [ W_uv,a o~_a(i) ]_a
+
+so that every head attends over the same rows c(j): attention with one shared key/value head of
+size kv_rank whose keys ARE its values, in prompt portions and in decoding alike, and a cached
+token costs kv_rank values whatever the number of heads.  There is no position encoding inside
+the mixer.  Sizes, the scale and the norms' eps are parameters.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..errors import KernelError
+from ..kernels import ops
+from .base import Mixer, PlanWish, RowNeed, register_mixer
+from .spec import TensorSpec
+
+
+class LatentAttention(Mixer):
+    graph_safe = True
+
+    def __init__(self, spec, rt, position_encodings=None):
+        super().__init__(spec, rt)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.heads, self.dim, self.vdim = int(p["heads"]), int(p["dim"]), int(p["vdim"])
+        self.q_rank, self.kv_rank = int(p["q_rank"]), int(p["kv_rank"])
+        self.scale, self.eps = float(p["scale"]), float(p["eps"])
+        # tensor leaves under the prefix: down / up projections, their norms' gains, the output projection
+        self.names = dict(dq="dq", dq_norm="dq.norm", uq="uq", dkv="dkv", dkv_norm="dkv.norm", uk="uk", uv="uv", o="o")
+        self.names.update(p.get("names", {}))
+        self.w_down = self.w_uq = self.w_uk = self.w_uv = self.w_o = self.g_q = self.g_kv = None
+        self._need = None
+
+    def tensors(self):
+        n, H, W = self.names, self.heads, self.hidden
+        return [TensorSpec(self._name(n["dq"]), (self.q_rank, W)), TensorSpec(self._name(n["dq_norm"]), (self.q_rank,), "gain"),
+                TensorSpec(self._name(n["uq"]), (H * self.dim, self.q_rank)),
+                TensorSpec(self._name(n["dkv"]), (self.kv_rank, W)), TensorSpec(self._name(n["dkv_norm"]), (self.kv_rank,), "gain"),
+                TensorSpec(self._name(n["uk"]), (H * self.dim, self.kv_rank)),
+                TensorSpec(self._name(n["uv"]), (H * self.vdim, self.kv_rank)),
+                TensorSpec(self._name(n["o"]), (W, H * self.vdim))]
+
+    def bind(self, tensors):
+        n, H = self.names, self.heads
+        t = lambda k: tensors[self._name(n[k])]
+        self.w_down = torch.cat([t("dq"), t("dkv")], 0).contiguous()         # one product makes both latents
+        self.w_uq, self.w_o = t("uq"), t("o")
+        self.g_q, self.g_kv = t("dq_norm"), t("dkv_norm")
+        self.w_uk = t("uk").view(H, self.dim, self.kv_rank)                   # q~_a = q_a W_uk,a       [dim] x [dim, kv_rank]
+        self.w_uv = t("uv").view(H, self.vdim, self.kv_rank).transpose(1, 2).contiguous()   # o_a = o~_a W_uv,a^T  [kv_rank, vdim]
+
+    def cache_need(self):
+        if self._need is None:
+            self._need = RowNeed(self.kv_rank)
+        return self._need
+
+    def plan_wish(self, page_size: int):
+        tile = ops.latent_attention_tile_tokens(self.heads, self.kv_rank, self.rt.dtype)
+        return PlanWish(tile, ops.latent_attention_ctas_per_item(self.heads, self.kv_rank, self.rt.dtype), self.heads, self.kv_rank)
+
+    def forward(self, x, step, cache, writes_cache=True):
+        rows, gi = cache
+        g = step.groups[gi]
+        T, H, R = x.shape[0], self.heads, self.kv_rank
+        st = self.rt.status
+        qa = ops.linear(x, self.w_down, status=st)
+        cq = torch.empty((T, self.q_rank), dtype=x.dtype, device=x.device)
+        ops.latent_norm_write(qa, self.g_q, self.g_kv, self.eps, cq, rows if writes_cache else None, g.slots,
+                              self.q_rank, R, st)
+        q = ops.linear(cq, self.w_uq, status=st)
+        # per head, batched over views [H, T, .] of tensors laid out [T, H, .] (what the attention kernel reads and writes)
+        q_lat = torch.empty((T, H, R), dtype=x.dtype, device=x.device)
+        torch.bmm(q.view(T, H, self.dim).transpose(0, 1), self.w_uk, out=q_lat.transpose(0, 1))
+        o_lat = torch.empty_like(q_lat)
+        ops.latent_attention(q_lat, rows, g.block_tables, g.plan, o_lat, self.scale, st)
+        o = torch.empty((T, H * self.vdim), dtype=x.dtype, device=x.device)
+        torch.bmm(o_lat.transpose(0, 1), self.w_uv, out=o.view(T, H, self.vdim).transpose(0, 1))
+        out = ops.linear(o, self.w_o, status=st)
+        if self.rt.trace is not None:
+            for leaf, t in (("q", q), ("q_latent", q_lat), ("o_latent", o_lat), ("o.in", o), ("out", out)):
+                self.rt.record(self._name(leaf), t)
+        return out
+
+
+register_mixer("latent_attention", LatentAttention)

@@ -16,13 +16,17 @@ class RMSNorm(Norm):
         super().__init__(spec, rt)
         self.width = int(spec.params["width"])
         self.eps = float(spec.params["eps"])
+        self.leaf = spec.params.get("leaf", "weight")       # the gain's name under the prefix ("": the prefix is its name)
         self.gain = None
 
+    def _gain_name(self):
+        return self._name(self.leaf) if self.leaf else self.prefix
+
     def tensors(self):
-        return [TensorSpec(self._name("weight"), (self.width,), "gain")]
+        return [TensorSpec(self._gain_name(), (self.width,), "gain")]
 
     def bind(self, tensors):
-        self.gain = tensors[self._name("weight")]
+        self.gain = tensors[self._gain_name()]
 
     def forward(self, x, rows=None):
         n = rows.numel() if rows is not None else x.shape[0]
@@ -41,4 +45,33 @@ class RMSNorm(Norm):
         return out
 
 
+class StreamRMSNorm(RMSNorm):
+    """RMSNorm for a decoder whose residual stream stays float32.  Two uses: ``forward`` norms rows of
+    the float32 stream into the compute dtype (the model's last norm); ``add_into`` is the norm on a
+    sublayer's OUTPUT: stream += norm(a), with the stream's rounding to the compute dtype as a
+    by-product for the next sublayer's products."""
+
+    def forward(self, x, rows=None):
+        if x.dtype != torch.float32:
+            return super().forward(x, rows)
+        n = rows.numel() if rows is not None else x.shape[0]
+        out = torch.empty((n, self.width), dtype=self.rt.dtype, device=x.device)
+        ops.rmsnorm_from32(x, self.gain, self.eps, out, rows=rows)
+        self.rt.record(self._name("out"), out)
+        return out
+
+    def add_norm(self, residual, delta, rows=None):
+        if delta is not None:
+            raise ValueError("a float32 stream carries no pending addition: its blocks add their own outputs")
+        return self.forward(residual, rows)
+
+    def add_into(self, stream, a):
+        """stream (float32, in place) += norm(a) * gain; returns what the next sublayer reads: the
+        stream itself in a float32 engine, else its rounding to the compute dtype."""
+        h = None if a.dtype == torch.float32 else torch.empty_like(a)
+        ops.outnorm_add(stream, a, self.gain, self.eps, h)
+        return stream if h is None else h
+
+
 register_norm("rmsnorm", RMSNorm)
+register_norm("rmsnorm_stream32", StreamRMSNorm)

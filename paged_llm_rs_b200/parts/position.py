@@ -45,5 +45,28 @@ class NoPositionEncoding(PositionEncoding):
     pass
 
 
+class SinusoidalEncoding(PositionEncoding):
+    """An absolute position vector added to a float32 residual stream right behind the embedding:
+    entry 2i is sin(p f_i), entry 2i + 1 is cos(p f_i), f_i = base^(-2i / width).  The frequencies
+    are formed in float64 on the host and kept in float32; the angle p f_i is a float32 product
+    formed by the kernel, so no table bounds the positions."""
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        self.width = int(spec.params["width"])
+        self.base = float(spec.params.get("base", 10000.0))
+        if self.width % 2:
+            raise ValueError(f"width {self.width} must be even: a sine pairs with a cosine")
+        self.inv_freq = None
+
+    def at_embedding(self, hidden, step):
+        if self.inv_freq is None:
+            f = np.power(np.float64(self.base), -2.0 * np.arange(self.width // 2, dtype=np.float64) / self.width)
+            self.inv_freq = torch.from_numpy(f.astype(np.float32)).to(self.rt.device)
+        from ..kernels import ops
+        return ops.sinusoid_add(hidden, step.positions, self.inv_freq)
+
+
 register_position_encoding("rope", RotaryEncoding)
 register_position_encoding("none", NoPositionEncoding)
+register_position_encoding("sinusoidal", SinusoidalEncoding)

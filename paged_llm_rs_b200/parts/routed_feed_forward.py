@@ -1,0 +1,87 @@
+"""A mixture of gated feed-forward experts behind a softmax router.
+
+Per token, with h the input (all router arithmetic in float32):
+
+    s = softmax(W_r h)                       over every router output
+    choice = s + correction                  the correction steers the choice only
+    outputs form ``groups`` equal groups of neighbours; a group scores its largest choice;
+    only outputs of the ``keep`` best groups can be chosen
+    the ``top`` largest choices are taken; weight_k = s_k / (sum of the chosen s + 1e-20)
+    out = sum_k weight_k * E_k(h)  (+ S(h))
+
+E_k is expert k's down(silu(gate h) * up h); the LAST ``identity`` router outputs have no
+tensors and return h itself; S is an optional expert of the same form that every token uses.
+Counts, sizes and tensor leaves are parameters.  The router and the experts are kernels of
+this library (csrc/moe.cu); the shared expert runs as the dense gated feed-forward does.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from .base import FeedForward, register_feed_forward
+from .spec import TensorSpec
+
+
+class RoutedExperts(FeedForward):
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        p = spec.params
+        self.hidden, self.ff = int(p["hidden_size"]), int(p["expert_size"])
+        self.experts, self.identity, self.top = int(p["experts"]), int(p.get("identity", 0)), int(p["top"])
+        self.groups, self.keep = int(p.get("groups", 1)), int(p.get("keep", 1))
+        self.shared_ff = p.get("shared_size")
+        self.corrected = bool(p.get("correction", True))
+        outputs = self.experts + self.identity
+        if outputs % self.groups or self.keep > self.groups or self.top > self.keep * (outputs // self.groups):
+            raise ValueError(f"{outputs} router outputs, {self.groups} groups of which {self.keep} are kept, top {self.top}: "
+                             "these do not fit together")
+        self.names = dict(router="router", correction="correction", expert="e{}", gate="gate", up="up", down="down", shared="shared")
+        self.names.update(p.get("names", {}))
+        self.w_router = self.correction = self.w_gu = self.w_d = self.ws_gu = self.ws_d = None
+
+    def _expert(self, e: int, leaf: str) -> str:
+        return self._name(f"{self.names['expert'].format(e)}.{self.names[leaf]}")
+
+    def _shared(self, leaf: str) -> str:
+        return self._name(f"{self.names['shared']}.{self.names[leaf]}")
+
+    def tensors(self):
+        W, ff, outputs = self.hidden, self.ff, self.experts + self.identity
+        t = [TensorSpec(self._name(self.names["router"]), (outputs, W), "matrix32")]
+        if self.corrected:
+            t.append(TensorSpec(self._name(self.names["correction"]), (outputs,), "offset"))
+        for e in range(self.experts):
+            t += [TensorSpec(self._expert(e, "gate"), (ff, W)), TensorSpec(self._expert(e, "up"), (ff, W)),
+                  TensorSpec(self._expert(e, "down"), (W, ff))]
+        if self.shared_ff:
+            sf = int(self.shared_ff)
+            t += [TensorSpec(self._shared("gate"), (sf, W)), TensorSpec(self._shared("up"), (sf, W)),
+                  TensorSpec(self._shared("down"), (W, sf))]
+        return t
+
+    def bind(self, tensors):
+        self.w_router = tensors[self._name(self.names["router"])]
+        self.correction = tensors[self._name(self.names["correction"])] if self.corrected else None
+        # experts stacked: [E, 2 ff, W] (an expert's gate rows, then its up rows) and [E, W, ff]
+        self.w_gu = torch.stack([torch.cat([tensors[self._expert(e, "gate")], tensors[self._expert(e, "up")]], 0)
+                                 for e in range(self.experts)], 0).contiguous()
+        self.w_d = torch.stack([tensors[self._expert(e, "down")] for e in range(self.experts)], 0).contiguous()
+        if self.shared_ff:
+            self.ws_gu = torch.cat([tensors[self._shared("gate")], tensors[self._shared("up")]], 0)
+            self.ws_d = tensors[self._shared("down")]
+
+    def forward(self, x, step):
+        st = self.rt.status
+        ids, weights = ops.moe_route(x, self.w_router, self.correction, self.top, self.groups, self.keep)
+        shared = ops.linear(ops.linear_glu(x, self.ws_gu, status=st), self.ws_d, status=st) if self.shared_ff else None
+        out = ops.moe_experts(x, ids, weights, self.w_gu, self.w_d, shared)
+        if self.rt.trace is not None:
+            self.rt.record(self._name("router.ids"), ids)
+            self.rt.record(self._name("router.weights"), weights)
+            self.rt.record(self._name("out"), out)
+        return out
+
+
+register_feed_forward("routed_experts", RoutedExperts)

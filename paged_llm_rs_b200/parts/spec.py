@@ -23,6 +23,8 @@ class TensorSpec:
     role decides the dtype it is kept in:
       "matrix"  compute dtype (bfloat16 when serving, float32 on the 32-bit path)
       "gain"    float32 always (norm gains; an exact upcast from bfloat16)
+      "matrix32" float32 always (a matrix whose product is formed in float: a router)
+      "offset"  float32 always (a vector added to float values: a router's correction)
       "index"   int32 (integer tables)
       "keep"    as stored (a tensor stored in 32-bit stays so)
     """
@@ -47,7 +49,7 @@ class PartSpec:
 class LayerSpec:
     block: str  # arrangement, e.g. "prenorm_residual"
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]  # None: the layer has no feed-forward (for arrangements that allow it)
     norms: Dict[str, PartSpec]  # the norms the arrangement names, e.g. "mixer", "feed_forward"
     prefix: str = ""
 

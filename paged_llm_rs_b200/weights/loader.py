@@ -55,7 +55,7 @@ def check_tensors(specs: Iterable[TensorSpec], available: Dict[str, tuple]) -> N
 def _kept_dtype(role: str, stored: torch.dtype, compute_dtype: torch.dtype) -> torch.dtype:
     if role == "matrix":
         return compute_dtype
-    if role == "gain":
+    if role in ("gain", "matrix32", "offset"):
         return torch.float32
     if role == "index":
         return torch.int32

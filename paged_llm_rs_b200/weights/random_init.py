@@ -62,6 +62,8 @@ def random_tensors(model_spec, seed: int, dtype: torch.dtype = torch.bfloat16, d
             continue
         if s.role == "gain":
             t = 1.0 + gain_std * _standard_normal(seed, s.name, s.shape, device)
+        elif s.role == "offset":
+            t = gain_std * _standard_normal(seed, s.name, s.shape, device)
         elif s.role == "index":
             t = torch.zeros(s.shape, dtype=torch.int32, device=device)
         else:
