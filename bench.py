@@ -506,6 +506,74 @@ def other_shape(key, layers, pk, clocks, steps, warmup):
     return out
 
 
+# ---- the latent-attention / mixture-of-experts decoder beside the grouped-query dense one at equal size ------------
+# Sizes that resemble real layers: the widths of the 0.6B and of a 2B-class shape, sixteen heads of 128, a cached
+# latent of 256 values a token (against 8 kv heads x 128 x 2 = 2048), layers that alternate a dense gated
+# feed-forward with a routed one whose chosen experts together are as wide as the dense one.
+LATENT_SIZES = {
+    "1024": dict(width=1024, heads=16, dim=128, vdim=128, q_rank=512, kv_rank=256, ff=3072, experts=16, top=4, expert_ff=768,
+                 shared_ff=768, groups=(4, 2)),
+    "2048": dict(width=2048, heads=16, dim=128, vdim=128, q_rank=768, kv_rank=256, ff=6144, experts=32, top=4, expert_ff=1536,
+                 shared_ff=1536, groups=(8, 4)),
+}
+LATENT_VOCAB = 32768
+
+
+def latent_config(z, layers):
+    mix = dict(heads=z["heads"], dim=z["dim"], vdim=z["vdim"], q_rank=z["q_rank"], kv_rank=z["kv_rank"], scale=z["dim"] ** -0.5)
+    dense = dict(kind="dense", ff=z["ff"])
+    moe = dict(kind="moe", expert=dict(ff=z["expert_ff"]), shared=dict(ff=z["shared_ff"]),
+               router=dict(experts=z["experts"], identity=0, top=z["top"], groups=dict(count=z["groups"][0], keep=z["groups"][1])))
+    return dict(architecture="Surelorn", vocab=LATENT_VOCAB, width=z["width"], embedding=dict(scale=1.0), norm=dict(eps=1e-6),
+                layers=[dict(type="latent_attention", mixer=mix, mlp=dense if i % 2 == 0 else moe) for i in range(layers)])
+
+
+def latent_beside_dense(size, layers, pk, clocks, steps, warmup, prefill_only=False, decode_only=False, which="both"):
+    """Decode (batch 1, 8, 64 at context 4096) and the 2048-token prefill of the Surelorn shape ``size`` and of the Qwen3
+    shape of the same width, heads, feed-forward width, layers and vocabulary: tokens a second, side by side."""
+    import gc
+    import torch
+    from paged_llm_rs_b200 import Engine, write_random_model
+
+    z = LATENT_SIZES[size]
+    qwen = dict(SHAPE_0_6B, hidden_size=z["width"], intermediate_size=z["ff"], num_hidden_layers=layers,
+                num_attention_heads=z["heads"], num_key_value_heads=8, head_dim=z["dim"], vocab_size=LATENT_VOCAB,
+                tie_word_embeddings=False)
+    out = dict(size=size, layers=layers, vocab=LATENT_VOCAB, latent=dict(z))
+    for name, cfg in (("surelorn", latent_config(z, layers)), ("qwen3", qwen)):
+        if which not in ("both", name):
+            continue
+        tmp = tempfile.mkdtemp(prefix="pllm_bench_", dir=scratch_dir())
+        try:
+            model_dir = write_random_model(os.path.join(tmp, "model"), cfg, 0, device="cuda")
+            ctx = 4096
+            pages = 64 * (ctx // PAGE + 4) + (PREFILL_TOKENS + 1024) // PAGE + 64
+            eng = Engine(model_dir, dtype="bfloat16", block_size=PAGE, blocks=pages, max_batch=64, chunk=PREFILL_TOKENS,
+                         prefix_cache=False)
+            shutil.rmtree(tmp, ignore_errors=True)
+            runner = eng.runner
+            for g in runner.cache.groups:
+                g.pool.normal_(0.0, 1.0)
+            res = dict(weight_bytes=runner.weight_bytes(), cache_bytes_a_token=runner.cache.bytes_per_token())
+            if not prefill_only:
+                for b in (1, 8, 64):
+                    ms, launches, spread = decode_point(runner, b, ctx, max(5, steps // 2), warmup, clocks, repeats=4)
+                    res[f"decode_b{b}_tok_s"] = round(b / (spread["median_ms"] / 1e3), 1)
+                    res[f"decode_b{b}_ms"] = spread["median_ms"]
+                    res[f"decode_b{b}_launches"] = launches
+            if not decode_only:
+                pms, _ = prefill_point(runner, LATENT_VOCAB, clocks, repeats=4)
+                res["prefill_ms"] = round(pms, 3)
+                res["prefill_tok_s"] = round(PREFILL_TOKENS / (pms / 1e3), 1)
+            out[name] = res
+            del eng, runner
+        finally:
+            shutil.rmtree(tmp, ignore_errors=True)
+            gc.collect()
+            torch.cuda.empty_cache()
+    return out
+
+
 TRACE_KERNELS = {0: "(tcgen05 kernel)", 1: "embed", 2: "rmsnorm", 3: "swiglu", 4: "qk_norm_rope_kv", 5: "attention_generic", 6: "attention_reduce",
                  7: "attention_mma", 8: "attention_tma", 9: "skinny_gemm", 10: "sample_partial", 11: "sample_final", 12: "gemm_tcgen05", 13: "attention_tcgen05"}
 TRACE_FILES = ["elementwise", "qk_norm_rope_kv", "attention_generic", "attention_mma", "attention_decode_tma", "sampling",
@@ -656,12 +724,18 @@ def main(argv=None) -> int:
                     help="with --only timeline: the captured step of a 2048-token prompt portion instead of the decode step")
     ap.add_argument("--timeline-mixed", type=int, default=0, metavar="TOKENS",
                     help="with --only timeline: the decoding requests beside one prompt portion of this many tokens")
-    ap.add_argument("--only", choices=["decode", "prefill", "long-prompt", "timeline", "reference-kernel", "plain-cpu"], default=None,
+    ap.add_argument("--latent-size", choices=sorted(LATENT_SIZES), default="1024",
+                    help="with --only latent: the width of the latent-attention / mixture-of-experts shape")
+    ap.add_argument("--latent-part", choices=["all", "decode", "prefill"], default="all", help="with --only latent: one part alone")
+    ap.add_argument("--latent-model", choices=["both", "surelorn", "qwen3"], default="both", help="with --only latent: one model alone")
+    ap.add_argument("--only", choices=["decode", "prefill", "long-prompt", "timeline", "reference-kernel", "plain-cpu", "latent"], default=None,
                     help="run one part alone and print a short line (for profiling; not a bench record); "
                          "long-prompt: a prompt of --context tokens in portions of 2048, each portion timed; "
                          "timeline: one captured decode step as the kernels themselves clocked it; reference-kernel: "
                          "the reference's CUDA kernel against this engine's decode attention; plain-cpu: the plain "
-                         "float32 implementation timed on the CPU (needs no GPU)")
+                         "float32 implementation timed on the CPU (needs no GPU); latent: decode and prefill of the "
+                         "latent-attention / mixture-of-experts decoder (Surelorn) beside the Qwen3 shape of equal size "
+                         "(--latent-size, --layers, default 8)")
     args = ap.parse_args(argv)
 
     if args.impl == "reference":
@@ -686,6 +760,14 @@ def main(argv=None) -> int:
 
     pk = peaks()
     clocks = ClockSampler()
+    if args.only == "latent":
+        clocks.start()
+        out = latent_beside_dense(args.latent_size, args.layers or 8, pk, clocks, steps, warmup,
+                                  prefill_only=args.latent_part == "prefill", decode_only=args.latent_part == "decode",
+                                  which=args.latent_model)
+        out["clocks"] = clocks.stop()
+        print(json.dumps(out))
+        return 0
     if args.only == "reference-kernel":
         clocks.start()
         out = reference_kernel_points(clocks)

@@ -65,7 +65,7 @@ template <int HD> __device__ __forceinline__ uint32_t tile_off(int row, int chun
     return (uint32_t)(row * (HD * 2) + ((chunk ^ (row & 7)) << 4));
 }
 
-template <int HD>
+template <int HD, bool SHARED = false>
 struct TileLoader {
     // Loads keys [kv0, kv0 + MMA_BK) of the item into one stage.  Thread t copies chunk
     // t % CH of rows t / CH + k * RPP.
@@ -94,13 +94,15 @@ struct TileLoader {
             }
             const uint32_t off = tile_off<HD>(row, chunk);
             cp_async16(k_s + off, k_pool + base, valid);
-            cp_async16(v_s + off, v_pool + base, valid);
+            if (!SHARED) cp_async16(v_s + off, v_pool + base, valid);
         }
     }
 };
 
-template <int HD>
-__global__ void __launch_bounds__(128, 2) attention_mma_kernel(
+// SHARED: keys and values are the same rows (attention over one cached latent row a token, every head
+// in the one group): a tile is brought once and read both ways, and a stage is half as large.
+template <int HD, bool SHARED = false>
+__global__ void __launch_bounds__(128, HD <= 128 ? 2 : 1) attention_mma_kernel(
     const bf16* q, const bf16* k_pool, const bf16* v_pool,   // written by the kernels before this one: no __restrict__
     const int* __restrict__ block_tables, const AttnWork* __restrict__ work, const int* __restrict__ n_work_ptr,
     bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
@@ -120,12 +122,13 @@ __global__ void __launch_bounds__(128, 2) attention_mma_kernel(
     constexpr int CH = HD / 8;
     constexpr int KSTEPS = HD / 16;                // k-steps of q.k^T
     constexpr int DTILES = HD / 8;                 // 8-wide output tiles of p.v
-    constexpr int STAGE_BYTES = 2 * MMA_BK * HD * 2;
+    constexpr int STAGE_BYTES = (SHARED ? 1 : 2) * MMA_BK * HD * 2;
+    constexpr bool Q_HELD = HD <= 128;             // wider rows: the query fragments are fetched anew at every k-step
 
     extern __shared__ __align__(128) unsigned char smem[];
     const uint32_t smem_base = smem_u32(smem);
 
-    TileLoader<HD> loader{k_pool, v_pool, block_tables + (size_t)w.seg * table_width, table_width, page_size, page_shift,
+    TileLoader<HD, SHARED> loader{k_pool, v_pool, block_tables + (size_t)w.seg * table_width, table_width, page_size, page_shift,
                           n_pages, nkv, kh, w.kv_end, swizzle ? 7 : 0};
     if (!(kinds_mask & (w.q_count == 1 ? 1 : 2))) return;   // the bulk-copy kernel takes these items
 
@@ -142,19 +145,17 @@ __global__ void __launch_bounds__(128, 2) attention_mma_kernel(
     const int n_tiles = (w.kv_end - w.kv_begin + MMA_BK - 1) / MMA_BK;
 #pragma unroll
     for (int s = 0; s < MMA_STAGES - 1; s++) {
-        if (s < n_tiles) loader.load(smem_base + s * STAGE_BYTES, smem_base + s * STAGE_BYTES + MMA_BK * HD * 2,
+        if (s < n_tiles) loader.load(smem_base + s * STAGE_BYTES, smem_base + s * STAGE_BYTES + (SHARED ? 0 : MMA_BK * HD * 2),
                                      w.kv_begin + s * MMA_BK, status);
         cp_async_commit();
     }
     cp_async_wait<MMA_STAGES - 1>();   // q has landed; the key tiles may still be in flight
     __syncthreads();
-    uint32_t qf[KSTEPS][4];
-    {
-        const int rbase = decode ? 0 : warp * 16;
-        const int mat = lane >> 3;
-        const int row = rbase + (lane & 7) + (mat & 1) * 8;
+    uint32_t qf[Q_HELD ? KSTEPS : 1][4];
+    const int q_row = (decode ? 0 : warp * 16) + (lane & 7) + ((lane >> 3) & 1) * 8;
+    if (Q_HELD) {
 #pragma unroll
-        for (int ks = 0; ks < KSTEPS; ks++) ldmatrix_x4(qf[ks], q_s + tile_off<HD>(row, ks * 2 + (mat >> 1)));
+        for (int ks = 0; ks < KSTEPS; ks++) ldmatrix_x4(qf[Q_HELD ? ks : 0], q_s + tile_off<HD>(q_row, ks * 2 + (lane >> 4)));
     }
 
     // ---- the two rows of this thread and what they may see -----------------------------------
@@ -193,13 +194,13 @@ __global__ void __launch_bounds__(128, 2) attention_mma_kernel(
             const int nt = t + MMA_STAGES - 1;
             if (nt < n_tiles) {
                 const uint32_t sb = smem_base + (nt % MMA_STAGES) * STAGE_BYTES;
-                loader.load(sb, sb + MMA_BK * HD * 2, w.kv_begin + nt * MMA_BK, status);
+                loader.load(sb, sb + (SHARED ? 0 : MMA_BK * HD * 2), w.kv_begin + nt * MMA_BK, status);
             }
             cp_async_commit();
         }
         const int kv0 = w.kv_begin + t * MMA_BK;
         if (kv0 + key_base >= warp_hi || kv0 + key_base + NT * 8 <= warp_lo) continue;
-        const uint32_t k_s = smem_base + (t % MMA_STAGES) * STAGE_BYTES, v_s = k_s + MMA_BK * HD * 2;
+        const uint32_t k_s = smem_base + (t % MMA_STAGES) * STAGE_BYTES, v_s = SHARED ? k_s : k_s + MMA_BK * HD * 2;
 
         // ---- scores: S[16 rows][NT*8 keys] ---------------------------------------------
         float s_acc[8][4];
@@ -215,14 +216,15 @@ __global__ void __launch_bounds__(128, 2) attention_mma_kernel(
 #pragma unroll
             for (int ks = 0; ks < KSTEPS; ks++) {
                 uint32_t kf[4][4];
+                if (!Q_HELD) ldmatrix_x4(qf[0], q_s + tile_off<HD>(q_row, ks * 2 + (lane >> 4)));
 #pragma unroll
                 for (int np = 0; np < 4; np++)
                     if (np < np_count) ldmatrix_x4(kf[np], k_s + tile_off<HD>(key0 + np * 16, ks * 2 + (mat & 1)));
 #pragma unroll
                 for (int np = 0; np < 4; np++) {
                     if (np >= np_count) break;
-                    mma_bf16(s_acc[np * 2], qf[ks], kf[np][0], kf[np][1]);
-                    mma_bf16(s_acc[np * 2 + 1], qf[ks], kf[np][2], kf[np][3]);
+                    mma_bf16(s_acc[np * 2], qf[Q_HELD ? ks : 0], kf[np][0], kf[np][1]);
+                    mma_bf16(s_acc[np * 2 + 1], qf[Q_HELD ? ks : 0], kf[np][2], kf[np][3]);
                 }
             }
         }
@@ -404,6 +406,43 @@ PLLM_EXPORT int pllm_attention_mma(const void* q, const void* k_pool, const void
                        window, scale_log2, heads_per_cta, swizzle, kinds_mask, status);
     }
     return launch_status();
+}
+
+// ---- the same kernel over ONE pool whose rows are keys and values at once --------------------------------
+// q, out: [tokens, heads, R]; pool: [pages, page_size, R] (one "kv head" that every query head reads).
+PLLM_EXPORT int pllm_latent_attention_mma_supports(int dtype, int heads, int R) {
+    return dtype == PLLM_BF16 && heads > 0 && (R == 64 || R == 128 || R == 256);
+}
+
+PLLM_EXPORT int pllm_latent_attention_mma_tile_tokens(int heads) { return MMA_ROWS / (heads < 16 ? heads : 16); }
+PLLM_EXPORT int pllm_latent_attention_mma_ctas_per_item(int heads) { return (heads + 15) / 16; }
+
+template <int R>
+static int launch_latent_mma(const void* q, const void* pool, const int* block_tables, const int* work, const int* n_work_ptr,
+                             int max_work, void* out, float* part_o, float* part_ml, int heads, int page_size, int n_pages,
+                             int table_width, float scale, int* status, cudaStream_t stream) {
+    const int heads_per_cta = heads < 16 ? heads : 16;
+    const int gparts = (heads + heads_per_cta - 1) / heads_per_cta;
+    int page_shift = -1;
+    if ((page_size & (page_size - 1)) == 0) { page_shift = 0; while ((1 << page_shift) < page_size) page_shift++; }
+    const int smem = MMA_STAGES * MMA_BK * R * 2 + MMA_ROWS * R * 2;
+    cudaFuncSetAttribute(attention_mma_kernel<R, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    launch_chained(attention_mma_kernel<R, true>, dim3(gparts, max_work), dim3(128), (size_t)smem, stream, (const bf16*)q,
+                   (const bf16*)pool, (const bf16*)pool, block_tables, (const AttnWork*)work, n_work_ptr, (bf16*)out, part_o,
+                   part_ml, heads, 1, page_size, page_shift, n_pages, table_width, 0, scale * 1.4426950408889634f,
+                   heads_per_cta, 0, 3, status);
+    return launch_status();
+}
+
+PLLM_EXPORT int pllm_latent_attention_mma(const void* q, const void* pool, const int* block_tables, const int* work,
+                                          const int* n_work_ptr, int max_work, void* out, float* part_o, float* part_ml,
+                                          int heads, int R, int page_size, int n_pages, int table_width, float scale,
+                                          int* status, cudaStream_t stream) {
+    if (max_work <= 0) return PLLM_OK;
+    if (!pllm_latent_attention_mma_supports(PLLM_BF16, heads, R) || page_size <= 0) return PLLM_ERR_SIZE;
+    if (R == 64) return launch_latent_mma<64>(q, pool, block_tables, work, n_work_ptr, max_work, out, part_o, part_ml, heads, page_size, n_pages, table_width, scale, status, stream);
+    if (R == 128) return launch_latent_mma<128>(q, pool, block_tables, work, n_work_ptr, max_work, out, part_o, part_ml, heads, page_size, n_pages, table_width, scale, status, stream);
+    return launch_latent_mma<256>(q, pool, block_tables, work, n_work_ptr, max_work, out, part_o, part_ml, heads, page_size, n_pages, table_width, scale, status, stream);
 }
 
 PLLM_TRACE_EXPORT(attention_mma)

@@ -44,7 +44,11 @@ template <int EPI, int BN>
 __global__ void __launch_bounds__(G_THREADS, 1) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                     const __grid_constant__ CUtensorMap map_b,
                                                                     bf16* __restrict__ y, int M, int n_out, int K,
-                                                                    int* status) {
+                                                                    int* status, const int* tile_expert, int expert_rows) {
+    // Grouped form (tile_expert given): the rows of x are sorted by expert, every expert's rows padded to whole
+    // tiles of 128; tile_expert[m tile] names the expert whose weights that tile multiplies (its rows of W start at
+    // expert * expert_rows), or is negative for a tile past the last one in use, which every role skips alike.
+    // The list is written by the kernel before this one: read after the wait for it, by plain loads.
     constexpr bool GLU = EPI == 1;
     constexpr int TILE_B = BN * G_BK * 2, STAGE = G_TILE_A + TILE_B;
     constexpr int STAGES = G_SMEM_TILES / STAGE;
@@ -94,6 +98,12 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tcgen05_kernel(const __grid
             bool ok = true;
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
                 const int m0 = (t % tiles_m) * G_BM, n0 = (t / tiles_m) * OUT_BN;
+                int w_row0 = 0;
+                if (tile_expert) {
+                    const int e = tile_expert[t % tiles_m];
+                    if (e < 0) continue;
+                    w_row0 = e * expert_rows;
+                }
                 for (int kb = 0; kb < k_blocks; kb++, it++) {
                     const int s = it % STAGES;
                     if (it >= STAGES && !mbar_wait(bars + 8 * (STAGES + s), ((it / STAGES) - 1) & 1, abort_flag)) { ok = false; break; }
@@ -101,10 +111,10 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tcgen05_kernel(const __grid
                     mbar_expect_tx(bars + 8 * s, STAGE);
                     tma_load_2d(a_dst, &map_a, kb * G_BK, m0, bars + 8 * s);
                     if (GLU) {
-                        tma_load_2d(b_dst, &map_b, kb * G_BK, n0, bars + 8 * s);                        // gate rows
-                        tma_load_2d(b_dst + TILE_B / 2, &map_b, kb * G_BK, n_out + n0, bars + 8 * s);   // up rows
+                        tma_load_2d(b_dst, &map_b, kb * G_BK, w_row0 + n0, bars + 8 * s);                        // gate rows
+                        tma_load_2d(b_dst + TILE_B / 2, &map_b, kb * G_BK, w_row0 + n_out + n0, bars + 8 * s);   // up rows
                     } else {
-                        tma_load_2d(b_dst, &map_b, kb * G_BK, n0, bars + 8 * s);
+                        tma_load_2d(b_dst, &map_b, kb * G_BK, w_row0 + n0, bars + 8 * s);
                     }
                 }
             }
@@ -115,7 +125,9 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tcgen05_kernel(const __grid
             constexpr uint32_t idesc = instr_desc(G_BM, BN);
             int it = 0, i = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, i++) {
+            if (tile_expert) asm volatile("griddepcontrol.wait;\n" ::: "memory");
+            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+                if (tile_expert && tile_expert[t % tiles_m] < 0) continue;
                 const int b = i & 1;
                 // the epilogue must have read this accumulator's last tile out
                 if (i >= 2 && !mbar_wait(acc_empty + 8 * b, ((i >> 1) - 1) & 1, abort_flag)) { ok = false; break; }
@@ -131,13 +143,16 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tcgen05_kernel(const __grid
                     mma_commit(bars + 8 * (STAGES + s));      // the stage is free once these have read it
                 }
                 if (ok) mma_commit(acc_full + 8 * b);         // this tile's accumulator is complete
+                i++;
             }
         }
     } else {
         // ---- epilogue: warp w owns lanes (rows) 32 w .. 32 w + 31 of the accumulators ---------------
         pdl_launch_dependents();
         int i = 0;
-        for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, i++) {
+        if (tile_expert) asm volatile("griddepcontrol.wait;\n" ::: "memory");
+        for (int t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+            if (tile_expert && tile_expert[t % tiles_m] < 0) continue;
             const int b = i & 1;
             const int m0 = (t % tiles_m) * G_BM, n0 = (t / tiles_m) * OUT_BN;
             if (!mbar_wait(acc_full + 8 * b, (i >> 1) & 1, abort_flag)) break;
@@ -179,6 +194,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tcgen05_kernel(const __grid
                         *reinterpret_cast<uint4*>(dst + k * 8) = make_uint4(out[4 * k], out[4 * k + 1], out[4 * k + 2], out[4 * k + 3]);
                 }
             }
+            i++;
         }
     }
     // ---- everyone meets; the allocating warp gives the tensor memory back ---------------------------
@@ -203,13 +219,13 @@ namespace {
 
 template <int EPI, int BN>
 int launch_gemm(const void* x, const void* w, void* y, int M, int n_out, int K, int* status,
-                cudaStream_t stream) {
+                cudaStream_t stream, const int* tile_expert = nullptr, int n_experts = 1) {
     constexpr bool GLU = EPI == 1;
     constexpr int OUT_BN = GLU ? BN / 2 : BN;
     constexpr int STAGE = G_TILE_A + BN * G_BK * 2, STAGES = G_SMEM_TILES / STAGE;
     CUtensorMap map_a, map_b;
     {
-        const long long da[2] = {K, M}, db[2] = {K, GLU ? 2LL * n_out : n_out}, st[1] = {2LL * K};
+        const long long da[2] = {K, M}, db[2] = {K, (long long)n_experts * (GLU ? 2LL * n_out : n_out)}, st[1] = {2LL * K};
         const int ba[2] = {G_BK, G_BM}, bb[2] = {G_BK, OUT_BN};
         if (tensor_map(x, 2, da, st, ba, true, &map_a) != 0) return PLLM_ERR_SIZE;
         if (tensor_map(w, 2, db, st, bb, true, &map_b) != 0) return PLLM_ERR_SIZE;
@@ -219,7 +235,8 @@ int launch_gemm(const void* x, const void* w, void* y, int M, int n_out, int K, 
     const int n_tiles = ((M + G_BM - 1) / G_BM) * (n_out / OUT_BN);
     const dim3 grid(n_tiles < g_sm_count ? n_tiles : g_sm_count);
     cudaFuncSetAttribute(gemm_tcgen05_kernel<EPI, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    launch_chained(gemm_tcgen05_kernel<EPI, BN>, grid, dim3(G_THREADS), smem, stream, map_a, map_b, (bf16*)y, M, n_out, K, status);
+    launch_chained(gemm_tcgen05_kernel<EPI, BN>, grid, dim3(G_THREADS), smem, stream, map_a, map_b, (bf16*)y, M, n_out, K, status,
+                   tile_expert, GLU ? 2 * n_out : n_out);
     return launch_status();
 }
 
@@ -239,6 +256,22 @@ PLLM_EXPORT int pllm_gemm_tcgen05(const void* x, const void* w, void* y, int M, 
                     : launch_gemm<1, 128>(x, w, y, M, n_out, K, status, stream);
     return wide ? launch_gemm<0, 256>(x, w, y, M, n_out, K, status, stream)
                 : launch_gemm<0, 128>(x, w, y, M, n_out, K, status, stream);
+}
+
+// The grouped form: x [M, K] holds the rows sorted by expert, each expert's rows padded to whole tiles of 128
+// (M a multiple of 128, an upper bound); w [experts, n_out (glu: 2 n_out), K]; tile_expert [M / 128] on the device.
+PLLM_EXPORT int pllm_gemm_tcgen05_grouped(const void* x, const void* w, void* y, int M, int n_out, int K, int glu,
+                                          const int* tile_expert, int n_experts, int* status, cudaStream_t stream) {
+    if (!pllm_gemm_tcgen05_supports(M, n_out, K, glu) || M % G_BM || n_experts < 1 || !tile_expert) return PLLM_ERR_SIZE;
+    if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15) return PLLM_ERR_ALIGN;
+    const int tiles_m = M / G_BM;
+    const int unit = glu ? 128 : 256;
+    const bool wide = n_out % unit == 0 && (long long)tiles_m * (n_out / unit) >= sm_count();
+    if (glu)
+        return wide ? launch_gemm<1, 256>(x, w, y, M, n_out, K, status, stream, tile_expert, n_experts)
+                    : launch_gemm<1, 128>(x, w, y, M, n_out, K, status, stream, tile_expert, n_experts);
+    return wide ? launch_gemm<0, 256>(x, w, y, M, n_out, K, status, stream, tile_expert, n_experts)
+                : launch_gemm<0, 128>(x, w, y, M, n_out, K, status, stream, tile_expert, n_experts);
 }
 
 PLLM_TRACE_EXPORT(gemm_tcgen05)

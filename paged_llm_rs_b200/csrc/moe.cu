@@ -246,4 +246,114 @@ PLLM_EXPORT int pllm_moe_pair_down(int dtype, const void* act, const void* h, co
     return launch_status();
 }
 
+// ---- the experts for many rows: sort the pairs by expert, grouped tensor-core products, combine ----------------
+// align:   slot_pair[slot] = pair or -1, pair_slot[pair] = slot or -1 (identity expert), tile_expert[tile] = expert or -1.
+//          Expert e's pairs take consecutive slots from a multiple of 128 on; which pair gets which of them is
+//          whatever order the atomics fall in, which changes no value: every row is multiplied on its own.
+// gather:  xs[slot] = h[pair / top]  (zeros in the padding of a tile in use; tiles past the last are left alone)
+// combine: out[t] = sum_k w[t, k] * (y[pair_slot] | h[t] for an identity expert) (+ shared[t])
+__global__ void __launch_bounds__(1024) moe_align_kernel(const int* ids, int n_pairs, int experts, int* __restrict__ slot_pair,
+                                                         int* __restrict__ pair_slot, int* __restrict__ tile_expert, int max_tiles) {
+    __shared__ int count[MOE_MAX_OUTPUTS], start[MOE_MAX_OUTPUTS];
+    pdl_launch_dependents();
+    pdl_wait(KID_MOE);
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
+    for (int i = threadIdx.x; i < max_tiles * 128; i += blockDim.x) slot_pair[i] = -1;
+    for (int i = threadIdx.x; i < max_tiles; i += blockDim.x) tile_expert[i] = -1;
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+        const int e = ids[p];
+        if (e >= 0 && e < experts) atomicAdd(&count[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int tile = 0;
+        for (int e = 0; e < experts; e++) {
+            start[e] = tile * 128;
+            const int tiles = (count[e] + 127) / 128;
+            for (int k = 0; k < tiles && tile + k < max_tiles; k++) tile_expert[tile + k] = e;
+            tile += tiles;
+            count[e] = 0;
+        }
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+        const int e = ids[p];
+        int slot = -1;
+        if (e >= 0 && e < experts) {
+            slot = start[e] + atomicAdd(&count[e], 1);
+            if (slot < max_tiles * 128) slot_pair[slot] = p; else slot = -1;
+        }
+        pair_slot[p] = slot;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) moe_gather_kernel(const T* h, const int* slot_pair, const int* tile_expert, T* __restrict__ xs,
+                                                         int n_slots, int width, int top) {
+    pdl_launch_dependents();
+    pdl_wait(KID_MOE);
+    const int lane = threadIdx.x & 31, slot = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (slot >= n_slots || tile_expert[slot >> 7] < 0) return;
+    const int pair = slot_pair[slot];
+    T* dst = xs + (size_t)slot * width;
+    constexpr int N = Vec16<T>::N;
+    if (pair < 0) {
+        for (int c = lane; c < width; c += 32) dst[c] = from_f32<T>(0.f);
+        return;
+    }
+    const T* src = h + (size_t)(pair / top) * width;
+    if (width % N == 0) {
+        for (int c = lane * N; c < width; c += 32 * N) { Vec16<T> v; v.load(src + c); v.store(dst + c); }
+    } else {
+        for (int c = lane; c < width; c += 32) dst[c] = src[c];
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) moe_combine_kernel(const T* y, const T* h, const int* pair_slot, const float* weights,
+                                                          const T* shared, T* __restrict__ out, int width, int top) {
+    pdl_launch_dependents();
+    pdl_wait(KID_MOE);
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float total = shared ? to_f32(shared[(size_t)t * width + c]) : 0.f;
+        for (int k = 0; k < top; k++) {
+            const int slot = pair_slot[(size_t)t * top + k];
+            const float v = slot < 0 ? to_f32(h[(size_t)t * width + c]) : to_f32(y[(size_t)slot * width + c]);
+            total = fmaf(weights[(size_t)t * top + k], v, total);
+        }
+        out[(size_t)t * width + c] = from_f32<T>(total);
+    }
+}
+
+PLLM_EXPORT int pllm_moe_align(const int* ids, int n_pairs, int experts, int* slot_pair, int* pair_slot, int* tile_expert,
+                               int max_tiles, cudaStream_t stream) {
+    if (n_pairs <= 0) return PLLM_OK;
+    if (experts <= 0 || max_tiles <= 0) return PLLM_ERR_SIZE;
+    if (experts > MOE_MAX_OUTPUTS) return PLLM_ERR_LIMIT;
+    launch_chained(moe_align_kernel, dim3(1), dim3(1024), 0, stream, ids, n_pairs, experts, slot_pair, pair_slot, tile_expert, max_tiles);
+    return launch_status();
+}
+
+PLLM_EXPORT int pllm_moe_gather(int dtype, const void* h, const int* slot_pair, const int* tile_expert, void* xs, int n_slots,
+                                int width, int top, cudaStream_t stream) {
+    if (n_slots <= 0) return PLLM_OK;
+    PLLM_DISPATCH_DTYPE(dtype, {
+        launch_chained(moe_gather_kernel<T>, dim3((n_slots + 7) / 8), dim3(256), 0, stream, (const T*)h, slot_pair, tile_expert,
+                       (T*)xs, n_slots, width, top);
+    });
+    return launch_status();
+}
+
+PLLM_EXPORT int pllm_moe_combine(int dtype, const void* y, const void* h, const int* pair_slot, const float* weights,
+                                 const void* shared, void* out, int n_tokens, int width, int top, cudaStream_t stream) {
+    if (n_tokens <= 0) return PLLM_OK;
+    PLLM_DISPATCH_DTYPE(dtype, {
+        launch_chained(moe_combine_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, (const T*)y, (const T*)h, pair_slot, weights,
+                       (const T*)shared, (T*)out, width, top);
+    });
+    return launch_status();
+}
+
 PLLM_TRACE_EXPORT(moe)

@@ -76,7 +76,15 @@ def lib():
         sig["pllm_latent_attention_generic_tile_tokens"] = [c_int]
         sig["pllm_latent_attention_generic_ctas_per_item"] = [c_int]
         sig["pllm_latent_attention_generic"] = [c_int, P, P, P, P, P, c_int, P, P, P] + [c_int] * 5 + [c_float, P, P]
+        sig["pllm_latent_attention_mma_supports"] = [c_int, c_int, c_int]
+        sig["pllm_latent_attention_mma_tile_tokens"] = [c_int]
+        sig["pllm_latent_attention_mma_ctas_per_item"] = [c_int]
+        sig["pllm_latent_attention_mma"] = [P, P, P, P, P, c_int, P, P, P] + [c_int] * 5 + [c_float, P, P]
         sig["pllm_moe_route"] = [c_int, P, P, P, P, P] + [c_int] * 6 + [P]
+        sig["pllm_moe_align"] = [P, c_int, c_int, P, P, P, c_int, P]
+        sig["pllm_moe_gather"] = [c_int, P, P, P, P, c_int, c_int, c_int, P]
+        sig["pllm_moe_combine"] = [c_int, P, P, P, P, P, P, c_int, c_int, c_int, P]
+        sig["pllm_gemm_tcgen05_grouped"] = [P, P, P, c_int, c_int, c_int, c_int, P, c_int, P, P]
         sig["pllm_moe_pair_glu"] = [c_int, P, P, P, P] + [c_int] * 5 + [P]
         sig["pllm_moe_pair_down"] = [c_int, P, P, P, P, P, P, P] + [c_int] * 5 + [P]
         sig["pllm_pack_decode_step"] = [P, c_int, c_int, P, P, P, P, P] + [c_int] * 16 + [P, P]
@@ -696,12 +704,26 @@ def latent_norm_write(qa: torch.Tensor, q_gain: torch.Tensor, kv_gain: torch.Ten
     return cq
 
 
+# PAGED_LLM_LATENT_MMA=0: the CUDA-core kernel everywhere (for comparisons)
+LATENT_MMA = os.environ.get("PAGED_LLM_LATENT_MMA", "1") != "0"
+
+
+def latent_attention_uses_tensor_cores(heads: int, kv_rank: int, dtype: torch.dtype) -> bool:
+    """bfloat16 with a latent of 64, 128 or 256 values: the mma.sync kernel of the grouped-query attention, with the
+    one pool read as keys and as values; everything else runs the CUDA-core kernel."""
+    return LATENT_MMA and dtype == torch.bfloat16 and bool(lib().pllm_latent_attention_mma_supports(_BF16, int(heads), int(kv_rank)))
+
+
 def latent_attention_tile_tokens(heads: int, kv_rank: int, dtype: torch.dtype) -> int:
-    """The most query tokens one work item of ``latent_attention`` may hold."""
+    """The most query tokens one work item of ``latent_attention`` may hold, for the kernel it picks."""
+    if latent_attention_uses_tensor_cores(heads, kv_rank, dtype):
+        return int(lib().pllm_latent_attention_mma_tile_tokens(int(heads)))
     return int(lib().pllm_latent_attention_generic_tile_tokens(int(heads)))
 
 
 def latent_attention_ctas_per_item(heads: int, kv_rank: int, dtype: torch.dtype) -> int:
+    if latent_attention_uses_tensor_cores(heads, kv_rank, dtype):
+        return int(lib().pllm_latent_attention_mma_ctas_per_item(int(heads)))
     return int(lib().pllm_latent_attention_generic_ctas_per_item(int(heads)))
 
 
@@ -725,9 +747,15 @@ def latent_attention(q: torch.Tensor, rows: torch.Tensor, block_tables: torch.Te
         raise KernelError("latent_attention: work / red lists shorter than their maxima")
     n_pages, page_size = rows.shape[0], rows.shape[1]
     L = lib()
-    _check(L.pllm_latent_attention_generic(_code(q), _ptr(q), _ptr(rows), _ptr(block_tables), _ptr(work), _ptr(n_work), max_work,
-                                           _ptr(out), _ptr(part_o), _ptr(part_ml), H, R, page_size, n_pages,
-                                           block_tables.shape[-1], float(scale), _ptr(status), _stream()), "latent_attention")
+    if latent_attention_uses_tensor_cores(H, R, q.dtype):
+        _check(L.pllm_latent_attention_mma(_ptr(q), _ptr(rows), _ptr(block_tables), _ptr(work), _ptr(n_work), max_work, _ptr(out),
+                                           _ptr(part_o), _ptr(part_ml), H, R, page_size, n_pages, block_tables.shape[-1],
+                                           float(scale), _ptr(status), _stream()), "latent_attention (mma)")
+    else:
+        _check(L.pllm_latent_attention_generic(_code(q), _ptr(q), _ptr(rows), _ptr(block_tables), _ptr(work), _ptr(n_work),
+                                               max_work, _ptr(out), _ptr(part_o), _ptr(part_ml), H, R, page_size, n_pages,
+                                               block_tables.shape[-1], float(scale), _ptr(status), _stream()),
+               "latent_attention")
     _check(L.pllm_attention_reduce(_code(q), _ptr(part_o), _ptr(part_ml), _ptr(red), _ptr(n_red), max_red, _ptr(out), H, R,
                                    1 if (w.many_splits and R * 4 <= 1024) else 0, _stream()), "attention_reduce")
     return out
@@ -772,7 +800,59 @@ def moe_experts_few(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w
     return out
 
 
+# Many rows in bfloat16: the pairs sorted by expert and the tcgen05 product in its grouped form (csrc/gemm_tcgen05.cu).
+# Below this many tokens a step's pairs are too few to fill tiles of 128 rows an expert, and the weight-streaming
+# form reads less.
+MOE_GROUPED_MIN_TOKENS = int(os.environ.get("PAGED_LLM_MOE_GROUPED_MIN", "48"))
+
+
+def moe_grouped_takes(h: torch.Tensor, w_gu: torch.Tensor, w_d: torch.Tensor) -> bool:
+    if h.dtype != torch.bfloat16 or h.shape[0] < MOE_GROUPED_MIN_TOKENS or TCGEN05_GEMM < 1:
+        return False
+    E, two_ff, W = w_gu.shape
+    L = lib()
+    return bool(L.pllm_gemm_tcgen05_supports(128, two_ff // 2, W, 1)) and bool(L.pllm_gemm_tcgen05_supports(128, W, two_ff // 2, 0))
+
+
+def moe_experts_grouped(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gu: torch.Tensor, w_d: torch.Tensor,
+                        shared: Optional[torch.Tensor], status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The same sum as ``moe_experts_few`` by sorting the (token, expert) pairs by expert, two grouped tensor-core
+    products (the first with the gated activation in its epilogue) and a weighted combine."""
+    _dev(h, ids, weights, w_gu, w_d, shared)
+    _i32(ids, "ids"); _f32(weights, "weights")
+    T, W = h.shape
+    E, two_ff, _ = w_gu.shape
+    ff, top = two_ff // 2, ids.shape[1]
+    if not moe_grouped_takes(h, w_gu, w_d) or w_gu.shape != (E, 2 * ff, W) or w_d.shape != (E, W, ff):
+        raise KernelError("moe_experts_grouped: shapes or dtypes the grouped product does not take")
+    n_pairs = T * top
+    max_tiles = -(-n_pairs // 128) + E
+    slots = max_tiles * 128
+    dev = h.device
+    slot_pair = torch.empty(slots, dtype=torch.int32, device=dev)
+    pair_slot = torch.empty(n_pairs, dtype=torch.int32, device=dev)
+    tile_expert = torch.empty(max_tiles, dtype=torch.int32, device=dev)
+    xs = torch.empty((slots, W), dtype=h.dtype, device=dev)
+    act = torch.empty((slots, ff), dtype=h.dtype, device=dev)
+    y = torch.empty((slots, W), dtype=h.dtype, device=dev)
+    out = torch.empty_like(h)
+    st = status if status is not None else gemm_status(dev)
+    L = lib()
+    _check(L.pllm_moe_align(_ptr(ids), n_pairs, E, _ptr(slot_pair), _ptr(pair_slot), _ptr(tile_expert), max_tiles, _stream()),
+           "moe_align")
+    _check(L.pllm_moe_gather(_code(h), _ptr(h), _ptr(slot_pair), _ptr(tile_expert), _ptr(xs), slots, W, top, _stream()), "moe_gather")
+    _check(L.pllm_gemm_tcgen05_grouped(_ptr(xs), _ptr(w_gu), _ptr(act), slots, ff, W, 1, _ptr(tile_expert), E, _ptr(st), _stream()),
+           "gemm_tcgen05_grouped (gate/up)")
+    _check(L.pllm_gemm_tcgen05_grouped(_ptr(act), _ptr(w_d), _ptr(y), slots, W, ff, 0, _ptr(tile_expert), E, _ptr(st), _stream()),
+           "gemm_tcgen05_grouped (down)")
+    _check(L.pllm_moe_combine(_code(h), _ptr(y), _ptr(h), _ptr(pair_slot), _ptr(weights), _ptr(shared), _ptr(out), T, W, top,
+                              _stream()), "moe_combine")
+    return out
+
+
 def moe_experts(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gu: torch.Tensor, w_d: torch.Tensor,
-                shared: Optional[torch.Tensor]) -> torch.Tensor:
+                shared: Optional[torch.Tensor], status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The routed experts' weighted sum (+ the shared expert's output), by the form that fits the step."""
+    if moe_grouped_takes(h, w_gu, w_d):
+        return moe_experts_grouped(h, ids, weights, w_gu, w_d, shared, status)
     return moe_experts_few(h, ids, weights, w_gu, w_d, shared)

@@ -76,7 +76,7 @@ class RoutedExperts(FeedForward):
         st = self.rt.status
         ids, weights = ops.moe_route(x, self.w_router, self.correction, self.top, self.groups, self.keep)
         shared = ops.linear(ops.linear_glu(x, self.ws_gu, status=st), self.ws_d, status=st) if self.shared_ff else None
-        out = ops.moe_experts(x, ids, weights, self.w_gu, self.w_d, shared)
+        out = ops.moe_experts(x, ids, weights, self.w_gu, self.w_d, shared, st)
         if self.rt.trace is not None:
             self.rt.record(self._name("router.ids"), ids)
             self.rt.record(self._name("router.weights"), weights)

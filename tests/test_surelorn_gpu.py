@@ -134,7 +134,8 @@ def test_router(dtype, outputs, top, groups, keep, corr):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("T,width,ff,experts,identity,top,shared", [
-    (5, 64, 48, 6, 0, 2, True), (3, 90, 30, 5, 3, 1, False), (70, 128, 64, 14, 2, 4, True), (1, 256, 128, 8, 0, 2, False)])
+    (5, 64, 48, 6, 0, 2, True), (3, 90, 30, 5, 3, 1, False), (70, 128, 64, 14, 2, 4, True), (1, 256, 128, 8, 0, 2, False),
+    (300, 256, 128, 8, 2, 3, True), (1000, 128, 192, 5, 0, 1, False), (64, 256, 64, 40, 0, 6, False)])
 def test_routed_experts_with_identity_and_shared(dtype, T, width, ff, experts, identity, top, shared):
     ops = ops_()
     g = torch.Generator().manual_seed(T)
@@ -224,7 +225,7 @@ def run_latent_attention(dtype, reqs, heads, R, page, target_ctas=296, craft=Non
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,R,page", [(3, 40, 16), (5, 36, 8), (20, 72, 16), (16, 128, 16), (6, 96, 64), (1, 8, 4), (2, 520, 16),
-                                          (16, 512, 16), (8, 64, 32)])
+                                          (16, 512, 16), (8, 64, 32), (16, 256, 16), (40, 128, 8), (12, 256, 32), (5, 64, 16)])
 def test_latent_attention_mixed_batch(dtype, heads, R, page):
     reqs = [(0, 1), (0, 37), (130, 1), (63, 2), (64, 5), (200, 1), (15, 17), (0, 2)]
     res, _ = run_latent_attention(dtype, reqs, heads, R, page)
@@ -233,7 +234,7 @@ def test_latent_attention_mixed_batch(dtype, heads, R, page):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads,R", [(3, 40), (16, 128), (20, 72)])
+@pytest.mark.parametrize("heads,R", [(3, 40), (16, 128), (20, 72), (16, 256)])
 def test_a_far_row_among_hundreds_decides(dtype, heads, R):
     """One cached row far back, at a page's border, pulls every head's query; without it the output is another."""
     page, ctx = 16, 700
