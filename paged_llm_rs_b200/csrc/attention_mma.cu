@@ -26,7 +26,7 @@
 #include "common.cuh"
 
 #define MMA_BK 64
-#define MMA_STAGES 3
+#define MMA_STAGES_MAX 3
 #define MMA_ROWS 64
 
 struct AttnWork { int seg, q_token0, q_count, q_pos0, kv_begin, kv_end, part_slot, split; };   // split: count << 16 | index (0: not split)
@@ -102,7 +102,7 @@ struct TileLoader {
 // SHARED: keys and values are the same rows (attention over one cached latent row a token, every head
 // in the one group): a tile is brought once and read both ways, and a stage is half as large.
 template <int HD, bool SHARED = false>
-__global__ void __launch_bounds__(128, HD <= 128 ? 2 : 1) attention_mma_kernel(
+__global__ void __launch_bounds__(128, 2) attention_mma_kernel(
     const bf16* q, const bf16* k_pool, const bf16* v_pool,   // written by the kernels before this one: no __restrict__
     const int* __restrict__ block_tables, const AttnWork* __restrict__ work, const int* __restrict__ n_work_ptr,
     bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
@@ -124,6 +124,7 @@ __global__ void __launch_bounds__(128, HD <= 128 ? 2 : 1) attention_mma_kernel(
     constexpr int DTILES = HD / 8;                 // 8-wide output tiles of p.v
     constexpr int STAGE_BYTES = (SHARED ? 1 : 2) * MMA_BK * HD * 2;
     constexpr bool Q_HELD = HD <= 128;             // wider rows: the query fragments are fetched anew at every k-step
+    constexpr int MMA_STAGES = HD <= 128 ? 3 : 2;  // ... and two tiles in flight instead of three, so that two CTAs share an SM
 
     extern __shared__ __align__(128) unsigned char smem[];
     const uint32_t smem_base = smem_u32(smem);
@@ -391,14 +392,14 @@ PLLM_EXPORT int pllm_attention_mma(const void* q, const void* k_pool, const void
     const float scale_log2 = scale * 1.4426950408889634f;
     dim3 grid(nkv * gparts, max_work);   // heads fastest: the items are dealt to the SMs in the order of the work list
     if (hd == 128) {
-        const int smem = MMA_STAGES * 2 * MMA_BK * 128 * 2 + MMA_ROWS * 128 * 2;
+        const int smem = MMA_STAGES_MAX * 2 * MMA_BK * 128 * 2 + MMA_ROWS * 128 * 2;
         cudaFuncSetAttribute(attention_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         launch_chained(attention_mma_kernel<128>, grid, dim3(128), (size_t)smem, stream,
                        (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_tables, (const AttnWork*)work,
                        n_work_ptr, (bf16*)out, part_o, part_ml, nh, nkv, page_size, page_shift, n_pages, table_width,
                        window, scale_log2, heads_per_cta, swizzle, kinds_mask, status);
     } else {
-        const int smem = MMA_STAGES * 2 * MMA_BK * 64 * 2 + MMA_ROWS * 64 * 2;
+        const int smem = MMA_STAGES_MAX * 2 * MMA_BK * 64 * 2 + MMA_ROWS * 64 * 2;
         cudaFuncSetAttribute(attention_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         launch_chained(attention_mma_kernel<64>, grid, dim3(128), (size_t)smem, stream,
                        (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_tables, (const AttnWork*)work,
@@ -425,7 +426,7 @@ static int launch_latent_mma(const void* q, const void* pool, const int* block_t
     const int gparts = (heads + heads_per_cta - 1) / heads_per_cta;
     int page_shift = -1;
     if ((page_size & (page_size - 1)) == 0) { page_shift = 0; while ((1 << page_shift) < page_size) page_shift++; }
-    const int smem = MMA_STAGES * MMA_BK * R * 2 + MMA_ROWS * R * 2;
+    const int smem = (R <= 128 ? 3 : 2) * MMA_BK * R * 2 + MMA_ROWS * R * 2;
     cudaFuncSetAttribute(attention_mma_kernel<R, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     launch_chained(attention_mma_kernel<R, true>, dim3(gparts, max_work), dim3(128), (size_t)smem, stream, (const bf16*)q,
                    (const bf16*)pool, (const bf16*)pool, block_tables, (const AttnWork*)work, n_work_ptr, (bf16*)out, part_o,

@@ -31,88 +31,132 @@ __device__ __forceinline__ void warp_argmax(float& best, int& at) {
     }
 }
 
-// One warp a token.  h in T (the float32 engine's h is float); router weights and correction float.
-template <typename T>
+// TOK tokens a CTA of four warps.  The tokens' rows lie in shared memory as floats; warp w forms the logits of router
+// outputs w, w + 4, ... for all of the CTA's tokens from one pass over each router row (float4 loads); then warp k
+// does the softmax, the groups and the choice for token k.  h in T (the float32 engine's h is float); router weights
+// and correction float.
+template <typename T, int TOK>
 __global__ void __launch_bounds__(128) moe_route_kernel(const T* h, const float* __restrict__ w_router,
                                                         const float* __restrict__ correction, int* __restrict__ ids,
                                                         float* __restrict__ weights, int n_tokens, int width, int outputs,
                                                         int top, int groups, int keep) {
-    extern __shared__ float smem[];      // per warp: s[outputs], choice[outputs], gscore[groups]
+    extern __shared__ float smem[];      // xs[TOK][width]; per token: s[outputs], choice[outputs], gscore[groups]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
-    float* s = smem + (size_t)warp * (2 * outputs + groups);
-    float* choice = s + outputs;
-    float* gscore = choice + outputs;
+    const int t0 = blockIdx.x * TOK;
+    float* xs = smem;
+    float* per_token = xs + (size_t)TOK * width;
+    const int per = 2 * outputs + groups;
     pdl_launch_dependents();
     pdl_wait(KID_MOE);
-    if (t >= n_tokens) return;
-    const T* hr = h + (size_t)t * width;
-    float zmax = -CUDART_INF_F;
-    for (int e = 0; e < outputs; e++) {
+    for (int i = threadIdx.x; i < TOK * width; i += blockDim.x) {
+        const int t = t0 + i / width;
+        xs[i] = t < n_tokens ? to_f32(h[(size_t)t * width + i % width]) : 0.f;
+    }
+    __syncthreads();
+    for (int e = warp; e < outputs; e += 4) {
         const float* wr = w_router + (size_t)e * width;
-        float acc = 0.f;
-        for (int c = lane; c < width; c += 32) acc = fmaf(to_f32(hr[c]), wr[c], acc);
-        acc = warp_sum(acc);
-        if (lane == 0) s[e] = acc;
-        zmax = fmaxf(zmax, acc);
+        float acc[TOK];
+#pragma unroll
+        for (int k = 0; k < TOK; k++) acc[k] = 0.f;
+        if (width % 4 == 0) {
+#pragma unroll 4
+            for (int c = lane * 4; c < width; c += 128) {
+                const float4 r = *reinterpret_cast<const float4*>(wr + c);
+#pragma unroll
+                for (int k = 0; k < TOK; k++) {
+                    const float4 x = *reinterpret_cast<const float4*>(xs + k * width + c);
+                    acc[k] = fmaf(x.x, r.x, fmaf(x.y, r.y, fmaf(x.z, r.z, fmaf(x.w, r.w, acc[k]))));
+                }
+            }
+        } else {
+            for (int c = lane; c < width; c += 32) {
+                const float r = wr[c];
+#pragma unroll
+                for (int k = 0; k < TOK; k++) acc[k] = fmaf(xs[k * width + c], r, acc[k]);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < TOK; k++) {
+            const float z = warp_sum(acc[k]);
+            if (lane == 0) per_token[k * per + e] = z;
+        }
     }
-    __syncwarp();
-    float sum = 0.f;
-    for (int e = lane; e < outputs; e += 32) { const float p = expf(s[e] - zmax); s[e] = p; sum += p; }
-    sum = warp_sum(sum);
-    __syncwarp();
-    for (int e = lane; e < outputs; e += 32) {
-        const float p = s[e] / sum;
-        s[e] = p;
-        choice[e] = p + (correction ? correction[e] : 0.f);
-    }
-    __syncwarp();
-    // groups: keep the best `keep`, the others' outputs cannot be chosen
-    if (groups > 1 && keep < groups) {
-        const int per = outputs / groups;
-        for (int g = lane; g < groups; g += 32) {
-            float gs = -CUDART_INF_F;
-            for (int j = 0; j < per; j++) gs = fmaxf(gs, choice[g * per + j]);
-            gscore[g] = gs;
+    __syncthreads();
+    for (int k = warp; k < TOK; k += 4) {
+        const int t = t0 + k;
+        if (t >= n_tokens) continue;
+        float* s = per_token + k * per;
+        float* choice = s + outputs;
+        float* gscore = choice + outputs;
+        float zmax = -CUDART_INF_F;
+        for (int e = lane; e < outputs; e += 32) zmax = fmaxf(zmax, s[e]);
+        zmax = warp_max(zmax);
+        float sum = 0.f;
+        for (int e = lane; e < outputs; e += 32) { const float p = expf(s[e] - zmax); s[e] = p; sum += p; }
+        sum = warp_sum(sum);
+        __syncwarp();
+        for (int e = lane; e < outputs; e += 32) {
+            const float p = s[e] / sum;
+            s[e] = p;
+            choice[e] = p + (correction ? correction[e] : 0.f);
         }
         __syncwarp();
-        for (int round = 0; round < keep; round++) {
-            float best = -CUDART_INF_F; int at = 0x7fffffff;
+        // groups: keep the best `keep`, the others' outputs cannot be chosen
+        if (groups > 1 && keep < groups) {
+            const int gsize = outputs / groups;
             for (int g = lane; g < groups; g += 32) {
-                const float gs = gscore[g];                    // (a kept group holds NaN and compares false)
-                if (gs > best || (gs == best && g < at)) { best = gs; at = g; }
+                float gs = -CUDART_INF_F;
+                for (int j = 0; j < gsize; j++) gs = fmaxf(gs, choice[g * gsize + j]);
+                gscore[g] = gs;
+            }
+            __syncwarp();
+            for (int round = 0; round < keep; round++) {
+                float best = -CUDART_INF_F; int at = 0x7fffffff;
+                for (int g = lane; g < groups; g += 32) {
+                    const float gs = gscore[g];                    // (a kept group holds NaN and compares false)
+                    if (gs > best || (gs == best && g < at)) { best = gs; at = g; }
+                }
+                warp_argmax(best, at);
+                __syncwarp();
+                if (lane == 0 && at != 0x7fffffff) gscore[at] = CUDART_NAN_F;
+                __syncwarp();
+            }
+            for (int e = lane; e < outputs; e += 32)
+                if (!isnan(gscore[e / gsize])) choice[e] = -CUDART_INF_F;
+            __syncwarp();
+        }
+        // the `top` best choice scores
+        float wsum = 0.f;
+        int mine_id = 0; float mine_s = 0.f;      // lane j holds the j-th choice (top <= 32)
+        for (int j = 0; j < top; j++) {
+            float best = -CUDART_INF_F; int at = 0x7fffffff;
+            for (int e = lane; e < outputs; e += 32) {
+                const float c = choice[e];
+                if (c > best) { best = c; at = e; }
             }
             warp_argmax(best, at);
+            if (at == 0x7fffffff) at = 0;          // (cannot happen for a valid configuration)
+            const float p = s[at];
+            wsum += p;
+            if (lane == j) { mine_id = at; mine_s = p; }
             __syncwarp();
-            if (lane == 0 && at != 0x7fffffff) gscore[at] = CUDART_NAN_F;
+            if (lane == 0) choice[at] = -CUDART_INF_F;
             __syncwarp();
         }
-        for (int e = lane; e < outputs; e += 32)
-            if (!isnan(gscore[e / per])) choice[e] = -CUDART_INF_F;
-        __syncwarp();
-    }
-    // the `top` best choice scores
-    float wsum = 0.f;
-    int mine_id = 0; float mine_s = 0.f;      // lane k holds the k-th choice (top <= 32)
-    for (int k = 0; k < top; k++) {
-        float best = -CUDART_INF_F; int at = 0x7fffffff;
-        for (int e = lane; e < outputs; e += 32) {
-            const float c = choice[e];
-            if (c > best || (c == best && e < at && c > -CUDART_INF_F)) { best = c; at = e; }
+        if (lane < top) {
+            ids[(size_t)t * top + lane] = mine_id;
+            weights[(size_t)t * top + lane] = mine_s / (wsum + 1e-20f);
         }
-        warp_argmax(best, at);
-        if (at == 0x7fffffff) at = 0;          // (cannot happen for a valid configuration)
-        const float p = s[at];
-        wsum += p;
-        if (lane == k) { mine_id = at; mine_s = p; }
-        __syncwarp();
-        if (lane == 0) choice[at] = -CUDART_INF_F;
-        __syncwarp();
     }
-    if (lane < top) {
-        ids[(size_t)t * top + lane] = mine_id;
-        weights[(size_t)t * top + lane] = mine_s / (wsum + 1e-20f);
-    }
+}
+
+template <typename T, int TOK>
+static void launch_route(const void* h, const float* w_router, const float* correction, int* ids, float* weights, int n_tokens,
+                         int width, int outputs, int top, int groups, int keep, cudaStream_t stream) {
+    const size_t smem = ((size_t)TOK * width + (size_t)TOK * (2 * outputs + groups)) * sizeof(float);
+    cudaFuncSetAttribute(moe_route_kernel<T, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_chained(moe_route_kernel<T, TOK>, dim3((n_tokens + TOK - 1) / TOK), dim3(128), smem, stream, (const T*)h, w_router,
+                   correction, ids, weights, n_tokens, width, outputs, top, groups, keep);
 }
 
 PLLM_EXPORT int pllm_moe_route(int dtype, const void* h, const float* w_router, const float* correction, int* ids, float* weights,
@@ -120,11 +164,12 @@ PLLM_EXPORT int pllm_moe_route(int dtype, const void* h, const float* w_router, 
     if (n_tokens <= 0) return PLLM_OK;
     if (width <= 0 || outputs <= 0 || top <= 0 || groups <= 0 || keep <= 0 || outputs % groups || keep > groups) return PLLM_ERR_SIZE;
     if (outputs > MOE_MAX_OUTPUTS || top > MOE_MAX_TOP || top > outputs) return PLLM_ERR_LIMIT;
+    // eight tokens a CTA from some hundreds of tokens on (a router row is then read once for the eight), where they fit
+    const bool many = n_tokens >= 256 && (8 * (size_t)width + 8 * (size_t)(2 * outputs + groups)) * sizeof(float) <= 160 * 1024;
+    if (((size_t)width + 2 * outputs + groups) * sizeof(float) > 200 * 1024) return PLLM_ERR_LIMIT;
     PLLM_DISPATCH_DTYPE(dtype, {
-        const int warps = 4;
-        launch_chained(moe_route_kernel<T>, dim3((n_tokens + warps - 1) / warps), dim3(warps * 32),
-                       (size_t)warps * (2 * outputs + groups) * sizeof(float), stream, (const T*)h, w_router, correction, ids, weights,
-                       n_tokens, width, outputs, top, groups, keep);
+        if (many) launch_route<T, 8>(h, w_router, correction, ids, weights, n_tokens, width, outputs, top, groups, keep, stream);
+        else launch_route<T, 1>(h, w_router, correction, ids, weights, n_tokens, width, outputs, top, groups, keep, stream);
     });
     return launch_status();
 }
@@ -155,6 +200,7 @@ __global__ void __launch_bounds__(256) moe_pair_glu_kernel(const T* h, const int
         const T* u = wu + (size_t)col * width;
         float ag = 0.f, au = 0.f;
         if (vec) {
+#pragma unroll 4
             for (int c = lane * N; c < width; c += 32 * N) {
                 Vec16<T> vg, vu; vg.load(g + c); vu.load(u + c);
                 float fg[N], fu[N]; vg.unpack(fg); vu.unpack(fu);
@@ -202,6 +248,7 @@ __global__ void __launch_bounds__(256) moe_pair_down_kernel(const T* act, const 
             const float* x = xs + k * ff;
             float acc = 0.f;
             if (vec) {
+#pragma unroll 4
                 for (int c = lane * N; c < ff; c += 32 * N) {
                     Vec16<T> vd; vd.load(d + c);
                     float fd[N]; vd.unpack(fd);
@@ -224,7 +271,8 @@ PLLM_EXPORT int pllm_moe_pair_glu(int dtype, const void* h, const int* ids, cons
     if (width <= 0 || ff <= 0 || top <= 0 || experts <= 0) return PLLM_ERR_SIZE;
     if ((size_t)width * sizeof(float) > 48 * 1024) return PLLM_ERR_LIMIT;
     PLLM_DISPATCH_DTYPE(dtype, {
-        const int cols = 64;
+        // a warp a column while the pairs are few (every SM gets CTAs), more columns a CTA as they grow
+        const int cols = n_tokens * top <= 64 ? 8 : 32;
         launch_chained(moe_pair_glu_kernel<T>, dim3(n_tokens * top, (ff + cols - 1) / cols), dim3(256), (size_t)width * sizeof(float),
                        stream, (const T*)h, ids, (const T*)w_gu, (T*)act, width, ff, top, experts, cols);
     });
@@ -238,7 +286,7 @@ PLLM_EXPORT int pllm_moe_pair_down(int dtype, const void* act, const void* h, co
     if (width <= 0 || ff <= 0 || top <= 0 || experts <= 0) return PLLM_ERR_SIZE;
     if ((size_t)top * ff * sizeof(float) > 48 * 1024) return PLLM_ERR_LIMIT;
     PLLM_DISPATCH_DTYPE(dtype, {
-        const int cols = 64;
+        const int cols = n_tokens <= 64 ? 8 : 32;
         launch_chained(moe_pair_down_kernel<T>, dim3(n_tokens, (width + cols - 1) / cols), dim3(256),
                        (size_t)top * ff * sizeof(float), stream, (const T*)act, (const T*)h, ids, weights, (const T*)w_d,
                        (const T*)shared, (T*)out, width, ff, top, experts, cols);

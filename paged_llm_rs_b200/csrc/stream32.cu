@@ -83,23 +83,37 @@ PLLM_EXPORT int pllm_round_rows(int dtype, const float* x, void* h, long long to
     return launch_status();
 }
 
-// One row a team of TEAM lanes x warps of a 256-thread CTA: the row of `a` is read once for the
-// statistic and once more (from L1) for the sum.  h may be null (a float32 engine reads x itself).
+// One row a team of 1 to 8 warps of a 256-thread CTA.  Rows of whole 16-byte vectors of T are read and written as
+// vectors (the stream as float4s beside them); the row of `a` is read once for the statistic and once more (from L1)
+// for the sum.  h may be null (a float32 engine reads x itself).
 template <typename T>
 __global__ void __launch_bounds__(256) outnorm_add_kernel(float* x, const T* a, const float* __restrict__ gain, T* h,
                                                           int n_rows, int width, float eps, int team) {
     __shared__ float part[8];
+    constexpr int N = Vec16<T>::N;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int member = (warp % team) * 32 + lane, lanes = team * 32;
     const int rows_per_cta = 8 / team;
     const int r = blockIdx.x * rows_per_cta + warp / team;
+    const bool vec = width % N == 0;
     pdl_launch_dependents();
     pdl_wait(KID_STREAM32);
     const bool live = r < n_rows;
     const T* ar = a + (size_t)(live ? r : 0) * width;
     float ss = 0.f;
-    if (live)
-        for (int c = member; c < width; c += lanes) { const float v = to_f32(ar[c]); ss += v * v; }
+    if (live) {
+        if (vec) {
+#pragma unroll 2
+            for (int c = member * N; c < width; c += lanes * N) {
+                Vec16<T> v; v.load(ar + c);
+                float f[N]; v.unpack(f);
+#pragma unroll
+                for (int k = 0; k < N; k++) ss += f[k] * f[k];
+            }
+        } else {
+            for (int c = member; c < width; c += lanes) { const float v = to_f32(ar[c]); ss += v * v; }
+        }
+    }
     ss = warp_sum(ss);
     if (team > 1) {
         if (lane == 0) part[warp] = ss;
@@ -112,6 +126,23 @@ __global__ void __launch_bounds__(256) outnorm_add_kernel(float* x, const T* a, 
     const float inv = 1.0f / sqrtf(ss / (float)width + eps);
     float* xr = x + (size_t)r * width;
     T* hr = h ? h + (size_t)r * width : nullptr;
+    if (vec) {
+#pragma unroll 2
+        for (int c = member * N; c < width; c += lanes * N) {
+            Vec16<T> v; v.load(ar + c);
+            float f[N]; v.unpack(f);
+#pragma unroll
+            for (int k = 0; k < N; k += 4) {
+                float4 s4 = *reinterpret_cast<float4*>(xr + c + k);
+                const float4 g4 = *reinterpret_cast<const float4*>(gain + c + k);
+                s4.x += f[k] * inv * g4.x; s4.y += f[k + 1] * inv * g4.y; s4.z += f[k + 2] * inv * g4.z; s4.w += f[k + 3] * inv * g4.w;
+                *reinterpret_cast<float4*>(xr + c + k) = s4;
+                f[k] = s4.x; f[k + 1] = s4.y; f[k + 2] = s4.z; f[k + 3] = s4.w;
+            }
+            if (hr) { Vec16<T> o; o.pack(f); o.store(hr + c); }
+        }
+        return;
+    }
     for (int c = member; c < width; c += lanes) {
         const float v = xr[c] + to_f32(ar[c]) * inv * gain[c];
         xr[c] = v;
@@ -119,13 +150,20 @@ __global__ void __launch_bounds__(256) outnorm_add_kernel(float* x, const T* a, 
     }
 }
 
+// warps a row: a lane holds two vectors or so; few rows get more warps each
+static inline int stream32_team(int n_rows, int width, int vec) {
+    const int per_lane = n_rows <= 64 ? vec : 2 * vec;
+    int team = 1;
+    while (team < 8 && width > team * 32 * per_lane) team *= 2;
+    return team;
+}
+
 PLLM_EXPORT int pllm_outnorm_add(int dtype, float* x, const void* a, const float* gain, void* h, int n_rows, int width,
                                  float eps, cudaStream_t stream) {
     if (n_rows <= 0) return PLLM_OK;
     if (width <= 0) return PLLM_ERR_SIZE;
     PLLM_DISPATCH_DTYPE(dtype, {
-        int team = 1;
-        while (team < 8 && width > team * 32 * 16) team *= 2;      // some sixteen elements a lane before a row gets more warps
+        const int team = stream32_team(n_rows, width, Vec16<T>::N);
         const int rows_per_cta = 8 / team;
         launch_chained(outnorm_add_kernel<T>, dim3((n_rows + rows_per_cta - 1) / rows_per_cta), dim3(256), 0, stream, x,
                        (const T*)a, gain, (T*)h, n_rows, width, eps, team);
@@ -148,8 +186,18 @@ __global__ void __launch_bounds__(256) rmsnorm_from32_kernel(const float* x, con
     const size_t r = live ? (rows ? (size_t)rows[i] : (size_t)i) : 0;
     const float* xr = x + r * width;
     float ss = 0.f;
-    if (live)
-        for (int c = member; c < width; c += lanes) { const float v = xr[c]; ss += v * v; }
+    const bool vec = width % 8 == 0;
+    if (live) {
+        if (vec) {
+#pragma unroll 2
+            for (int c = member * 4; c < width; c += lanes * 4) {
+                const float4 v = *reinterpret_cast<const float4*>(xr + c);
+                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            }
+        } else {
+            for (int c = member; c < width; c += lanes) { const float v = xr[c]; ss += v * v; }
+        }
+    }
     ss = warp_sum(ss);
     if (team > 1) {
         if (lane == 0) part[warp] = ss;
@@ -161,6 +209,15 @@ __global__ void __launch_bounds__(256) rmsnorm_from32_kernel(const float* x, con
     if (!live) return;
     const float inv = 1.0f / sqrtf(ss / (float)width + eps);
     T* yr = y + (size_t)i * width;
+    if (vec) {
+        for (int c = member * 4; c < width; c += lanes * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(xr + c);
+            const float4 g = *reinterpret_cast<const float4*>(gain + c);
+            yr[c] = from_f32<T>(v.x * inv * g.x); yr[c + 1] = from_f32<T>(v.y * inv * g.y);
+            yr[c + 2] = from_f32<T>(v.z * inv * g.z); yr[c + 3] = from_f32<T>(v.w * inv * g.w);
+        }
+        return;
+    }
     for (int c = member; c < width; c += lanes) yr[c] = from_f32<T>(xr[c] * inv * gain[c]);
 }
 
@@ -169,8 +226,7 @@ PLLM_EXPORT int pllm_rmsnorm_from32(int dtype, const float* x, const float* gain
     if (n_rows <= 0) return PLLM_OK;
     if (width <= 0) return PLLM_ERR_SIZE;
     PLLM_DISPATCH_DTYPE(dtype, {
-        int team = 1;
-        while (team < 8 && width > team * 32 * 16) team *= 2;
+        const int team = stream32_team(n_rows, width, 4);
         const int rows_per_cta = 8 / team;
         launch_chained(rmsnorm_from32_kernel<T>, dim3((n_rows + rows_per_cta - 1) / rows_per_cta), dim3(256), 0, stream, x,
                        gain, (T*)y, rows, n_rows, width, eps, team);
