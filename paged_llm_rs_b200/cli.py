@@ -106,7 +106,7 @@ def main(argv=None) -> int:
     if dtype == "auto":  # the checkpoint's own dtype, read from the embedding (model/mod.rs:175)
         import torch
         files = open_model_files(args.model)
-        stored = next((f.dtype(n) for f in files for n in f.names() if n.endswith("embed_tokens.weight")), torch.bfloat16)
+        stored = next((f.dtype(n) for f in files for n in f.names() if n.endswith("embed_tokens.weight") or n == "embed"), torch.bfloat16)
         dtype = "f32" if stored == torch.float32 else "bf16"
     defaults = GenerationDefaults.from_dir(args.model)
     temperature = args.temperature if args.temperature is not None else (defaults.temperature or 0.0)

@@ -13,23 +13,72 @@ __global__ void __launch_bounds__(256) latent_norm_write_kernel(const T* qa, con
                                                                 const float* __restrict__ kv_gain, float eps, T* __restrict__ cq,
                                                                 T* pool, const int* __restrict__ slots, int q_rank, int kv_rank,
                                                                 long long pool_rows, int* status) {
-    __shared__ float scratch[32];
+    __shared__ float scratch[2][8];
     pdl_launch_dependents();
     const int t = blockIdx.x;
     const int slot = (pool && slots) ? slots[t] : -1;
     pdl_wait(KID_LATENT);
-    const T* row = qa + (size_t)t * (q_rank + kv_rank);
+    constexpr int N = Vec16<T>::N;
+    const int total = q_rank + kv_rank;
+    const T* row = qa + (size_t)t * total;
+    const bool vec = q_rank % N == 0 && kv_rank % N == 0;      // every vector lies in one of the two parts, rows start on 16 bytes
+    // a thread's share of the row stays in registers between the statistic and the scaling where it is a vector or two
+    float f[2][N];
     float sq = 0.f, sk = 0.f;
-    for (int c = threadIdx.x; c < q_rank; c += blockDim.x) { const float v = to_f32(row[c]); sq += v * v; }
-    for (int c = threadIdx.x; c < kv_rank; c += blockDim.x) { const float v = to_f32(row[q_rank + c]); sk += v * v; }
-    sq = block_sum(sq, scratch);
-    sk = block_sum(sk, scratch);
+    if (vec) {
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            const int c = (threadIdx.x + j * blockDim.x) * N;
+            if (c < total) {
+                Vec16<T> v; v.load(row + c); v.unpack(f[j]);
+                float ss = 0.f;
+#pragma unroll
+                for (int k = 0; k < N; k++) ss += f[j][k] * f[j][k];
+                if (c < q_rank) sq += ss; else sk += ss;
+            }
+        }
+        for (int c = (threadIdx.x + 2 * blockDim.x) * N; c < total; c += blockDim.x * N) {      // (rows wider than two vectors a thread)
+            Vec16<T> v; v.load(row + c);
+            float g[N]; v.unpack(g);
+            float ss = 0.f;
+#pragma unroll
+            for (int k = 0; k < N; k++) ss += g[k] * g[k];
+            if (c < q_rank) sq += ss; else sk += ss;
+        }
+    } else {
+        for (int c = threadIdx.x; c < total; c += blockDim.x) { const float v = to_f32(row[c]); if (c < q_rank) sq += v * v; else sk += v * v; }
+    }
+    sq = warp_sum(sq); sk = warp_sum(sk);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = (blockDim.x + 31) >> 5;
+    if (lane == 0) { scratch[0][warp] = sq; scratch[1][warp] = sk; }
+    __syncthreads();
+    sq = 0.f; sk = 0.f;
+    for (int w = 0; w < warps; w++) { sq += scratch[0][w]; sk += scratch[1][w]; }
     const float iq = 1.0f / sqrtf(sq / (float)q_rank + eps), ik = 1.0f / sqrtf(sk / (float)kv_rank + eps);
     T* cqr = cq + (size_t)t * q_rank;
+    const bool writes = slot >= 0 && slot < pool_rows;
+    if (slot >= pool_rows && threadIdx.x == 0) atomicOr(status, 2);      // (a negative slot: padding of a captured step, or a run that reads another run's cache)
+    T* dst = writes ? pool + (size_t)slot * kv_rank : nullptr;
+    if (vec) {
+        for (int j = 0, c = threadIdx.x * N; c < total; j++, c += blockDim.x * N) {
+            float g[N];
+            if (j < 2) {
+#pragma unroll
+                for (int k = 0; k < N; k++) g[k] = f[j][k];
+            } else { Vec16<T> v; v.load(row + c); v.unpack(g); }
+            const bool isq = c < q_rank;
+            const float* gain = isq ? q_gain + c : kv_gain + (c - q_rank);
+            const float inv = isq ? iq : ik;
+#pragma unroll
+            for (int k = 0; k < N; k++) g[k] = g[k] * inv * gain[k];
+            Vec16<T> o; o.pack(g);
+            if (isq) o.store(cqr + c);
+            else if (dst) o.store(dst + (c - q_rank));
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < q_rank; c += blockDim.x) cqr[c] = from_f32<T>(to_f32(row[c]) * iq * q_gain[c]);
-    if (slot < 0) return;                 // padding of a captured step, or a run that reads another run's cache
-    if (slot >= pool_rows) { if (threadIdx.x == 0) atomicOr(status, 2); return; }
-    T* dst = pool + (size_t)slot * kv_rank;
+    if (!dst) return;
     for (int c = threadIdx.x; c < kv_rank; c += blockDim.x) dst[c] = from_f32<T>(to_f32(row[q_rank + c]) * ik * kv_gain[c]);
 }
 
@@ -39,8 +88,7 @@ PLLM_EXPORT int pllm_latent_norm_write(int dtype, const void* qa, const float* q
     if (n_tokens <= 0) return PLLM_OK;
     if (q_rank <= 0 || kv_rank <= 0) return PLLM_ERR_SIZE;
     PLLM_DISPATCH_DTYPE(dtype, {
-        const int widest = q_rank > kv_rank ? q_rank : kv_rank;
-        const int threads = min(256, max(32, (widest / 4 + 31) / 32 * 32));
+        const int threads = min(256, max(32, ((q_rank + kv_rank) / Vec16<T>::N + 31) / 32 * 32));
         launch_chained(latent_norm_write_kernel<T>, dim3(n_tokens), dim3(threads), 0, stream, (const T*)qa, q_gain, kv_gain, eps,
                        (T*)cq, (T*)pool, slots, q_rank, kv_rank, pool_rows, status);
     });

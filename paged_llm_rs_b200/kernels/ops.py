@@ -721,9 +721,14 @@ def latent_attention_tile_tokens(heads: int, kv_rank: int, dtype: torch.dtype) -
     return int(lib().pllm_latent_attention_generic_tile_tokens(int(heads)))
 
 
+# How heavily a CTA of the tensor-core kernel counts when the step's attention is cut into splits: its CTAs hold
+# half an SM each and pay a fixed start and a combine through shared memory, so fewer, longer splits suit it.
+LATENT_CTA_WEIGHT = int(os.environ.get("PAGED_LLM_LATENT_CTA_WEIGHT", "1"))
+
+
 def latent_attention_ctas_per_item(heads: int, kv_rank: int, dtype: torch.dtype) -> int:
     if latent_attention_uses_tensor_cores(heads, kv_rank, dtype):
-        return int(lib().pllm_latent_attention_mma_ctas_per_item(int(heads)))
+        return int(lib().pllm_latent_attention_mma_ctas_per_item(int(heads))) * LATENT_CTA_WEIGHT
     return int(lib().pllm_latent_attention_generic_ctas_per_item(int(heads)))
 
 

@@ -109,9 +109,12 @@ class RowNeed(PagedNeed):
     kind: str = "full"
     window: Optional[int] = None
     dtype: Optional[torch.dtype] = None
+    # what else must be equal for two mixers to share a group (its block tables AND its attention work items):
+    # mixers whose kernels cut a step differently (another number of heads, say) give different keys
+    plan_key: tuple = ()
 
     def group_key(self) -> tuple:
-        return ("rows", self.kind, self.window, self.width, self.dtype)
+        return ("rows", self.kind, self.window, self.width, self.dtype, self.plan_key)
 
     def pool_shape(self, entries, pages, page_size):
         return (entries, pages, page_size, self.width)

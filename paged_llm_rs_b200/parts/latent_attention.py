@@ -67,7 +67,7 @@ class LatentAttention(Mixer):
 
     def cache_need(self):
         if self._need is None:
-            self._need = RowNeed(self.kv_rank)
+            self._need = RowNeed(self.kv_rank, plan_key=(self.heads,))      # (work items are cut by the number of heads)
         return self._need
 
     def plan_wish(self, page_size: int):

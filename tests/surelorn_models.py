@@ -49,7 +49,8 @@ SMALL = dict(architecture="Surelorn", vocab=200, width=64, embedding=dict(scale=
 # T: five heads, widths that are no multiple of eight, one expert a token with identity experts and no groups, no shared expert
 ODD = dict(architecture="Surelorn", vocab=333, width=90, embedding=dict(scale=2.5), norm=dict(eps=1e-5), layers=[
     layer(mixer(5, 12, 6, 36, 20), moe(5, 1, 30, identity=3)),
-    layer(mixer(5, 12, 6, 36, 20), dense(50))])
+    layer(mixer(5, 12, 6, 36, 20), dense(50)),
+    layer(mixer(2, 10, 14, 36, 12), dense(50))])         # the same latent width under another number of heads
 
 # U: more heads than one CTA's rows, four experts a token out of two kept groups of four, a shared expert of another width
 WIDE = dict(architecture="Surelorn", vocab=512, width=128, embedding=dict(scale=8.0), norm=dict(eps=1e-6), layers=[
