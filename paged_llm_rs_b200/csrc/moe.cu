@@ -31,12 +31,12 @@ __device__ __forceinline__ void warp_argmax(float& best, int& at) {
     }
 }
 
-// TOK tokens a CTA of four warps.  The tokens' rows lie in shared memory as floats; warp w forms the logits of router
-// outputs w, w + 4, ... for all of the CTA's tokens from one pass over each router row (float4 loads); then warp k
+// TOK tokens a CTA of eight warps.  The tokens' rows lie in shared memory as floats; warp w forms the logits of router
+// outputs w, w + 8, ... for all of the CTA's tokens from one pass over each router row (float4 loads); then warp k
 // does the softmax, the groups and the choice for token k.  h in T (the float32 engine's h is float); router weights
 // and correction float.
 template <typename T, int TOK>
-__global__ void __launch_bounds__(128) moe_route_kernel(const T* h, const float* __restrict__ w_router,
+__global__ void __launch_bounds__(256) moe_route_kernel(const T* h, const float* __restrict__ w_router,
                                                         const float* __restrict__ correction, int* __restrict__ ids,
                                                         float* __restrict__ weights, int n_tokens, int width, int outputs,
                                                         int top, int groups, int keep) {
@@ -48,18 +48,30 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const T* h, const float*
     const int per = 2 * outputs + groups;
     pdl_launch_dependents();
     pdl_wait(KID_MOE);
-    for (int i = threadIdx.x; i < TOK * width; i += blockDim.x) {
-        const int t = t0 + i / width;
-        xs[i] = t < n_tokens ? to_f32(h[(size_t)t * width + i % width]) : 0.f;
+    constexpr int N = Vec16<T>::N;
+    if (width % N == 0) {
+        for (int i = threadIdx.x * N; i < TOK * width; i += blockDim.x * N) {
+            const int t = t0 + i / width;
+            if (t < n_tokens) { Vec16<T> v; v.load(h + (size_t)t * width + i % width); v.unpack(xs + i); }
+            else {
+#pragma unroll
+                for (int k = 0; k < N; k++) xs[i + k] = 0.f;
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < TOK * width; i += blockDim.x) {
+            const int t = t0 + i / width;
+            xs[i] = t < n_tokens ? to_f32(h[(size_t)t * width + i % width]) : 0.f;
+        }
     }
     __syncthreads();
-    for (int e = warp; e < outputs; e += 4) {
+    for (int e = warp; e < outputs; e += 8) {
         const float* wr = w_router + (size_t)e * width;
         float acc[TOK];
 #pragma unroll
         for (int k = 0; k < TOK; k++) acc[k] = 0.f;
         if (width % 4 == 0) {
-#pragma unroll 4
+#pragma unroll 8
             for (int c = lane * 4; c < width; c += 128) {
                 const float4 r = *reinterpret_cast<const float4*>(wr + c);
 #pragma unroll
@@ -82,7 +94,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const T* h, const float*
         }
     }
     __syncthreads();
-    for (int k = warp; k < TOK; k += 4) {
+    for (int k = warp; k < TOK; k += 8) {
         const int t = t0 + k;
         if (t >= n_tokens) continue;
         float* s = per_token + k * per;
@@ -155,7 +167,7 @@ static void launch_route(const void* h, const float* w_router, const float* corr
                          int width, int outputs, int top, int groups, int keep, cudaStream_t stream) {
     const size_t smem = ((size_t)TOK * width + (size_t)TOK * (2 * outputs + groups)) * sizeof(float);
     cudaFuncSetAttribute(moe_route_kernel<T, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    launch_chained(moe_route_kernel<T, TOK>, dim3((n_tokens + TOK - 1) / TOK), dim3(128), smem, stream, (const T*)h, w_router,
+    launch_chained(moe_route_kernel<T, TOK>, dim3((n_tokens + TOK - 1) / TOK), dim3(256), smem, stream, (const T*)h, w_router,
                    correction, ids, weights, n_tokens, width, outputs, top, groups, keep);
 }
 
@@ -176,92 +188,138 @@ PLLM_EXPORT int pllm_moe_route(int dtype, const void* h, const float* w_router, 
 
 // ---- the experts for a few rows -----------------------------------------------------------------
 // w_gu: [experts, 2 * ff, width] (an expert's gate rows, then its up rows); act: [pairs, ff].
-// grid (pairs, column blocks); a CTA keeps the token's row in shared memory as floats.
+// grid (pairs, column blocks); a CTA keeps the token's row in shared memory as floats; a warp forms PAIR_CW columns
+// at a time, so that the loads of 2 * PAIR_CW weight rows are in flight together.
+#define PAIR_CW 4
 template <typename T>
 __global__ void __launch_bounds__(256) moe_pair_glu_kernel(const T* h, const int* ids, const T* __restrict__ w_gu, T* __restrict__ act,
-                                                           int width, int ff, int top, int experts, int cols_per_cta) {
+                                                           int width, int ff, int top, int experts) {
     extern __shared__ float xs[];
-    const int pair = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int pair = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     pdl_launch_dependents();
     pdl_wait(KID_MOE);
     const int e = ids[pair];
     if (e < 0 || e >= experts) return;             // an identity expert has no product
+    constexpr int N = Vec16<T>::N;
+    const bool vec = width % N == 0;
     const T* hr = h + (size_t)(pair / top) * width;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) xs[c] = to_f32(hr[c]);
+    if (vec) {
+        for (int c = threadIdx.x * N; c < width; c += blockDim.x * N) { Vec16<T> v; v.load(hr + c); v.unpack(xs + c); }
+    } else {
+        for (int c = threadIdx.x; c < width; c += blockDim.x) xs[c] = to_f32(hr[c]);
+    }
     __syncthreads();
     const T* wg = w_gu + (size_t)e * 2 * ff * width;
     const T* wu = wg + (size_t)ff * width;
-    const int col0 = blockIdx.y * cols_per_cta;
-    const int col1 = min(ff, col0 + cols_per_cta);
-    constexpr int N = Vec16<T>::N;
-    const bool vec = width % N == 0;
-    for (int col = col0 + warp; col < col1; col += warps) {
-        const T* g = wg + (size_t)col * width;
-        const T* u = wu + (size_t)col * width;
-        float ag = 0.f, au = 0.f;
-        if (vec) {
-#pragma unroll 4
-            for (int c = lane * N; c < width; c += 32 * N) {
-                Vec16<T> vg, vu; vg.load(g + c); vu.load(u + c);
-                float fg[N], fu[N]; vg.unpack(fg); vu.unpack(fu);
+    const int col0 = (blockIdx.y * 8 + warp) * PAIR_CW;
+    if (col0 >= ff) return;
+    float ag[PAIR_CW], au[PAIR_CW];
 #pragma unroll
-                for (int k = 0; k < N; k++) { ag = fmaf(xs[c + k], fg[k], ag); au = fmaf(xs[c + k], fu[k], au); }
+    for (int j = 0; j < PAIR_CW; j++) { ag[j] = 0.f; au[j] = 0.f; }
+    if (vec) {
+#pragma unroll 2
+        for (int c = lane * N; c < width; c += 32 * N) {
+            Vec16<T> vg[PAIR_CW], vu[PAIR_CW];
+#pragma unroll
+            for (int j = 0; j < PAIR_CW; j++) {
+                const int col = min(col0 + j, ff - 1);           // (a column past the end repeats the last one and is not stored)
+                vg[j].load(wg + (size_t)col * width + c); vu[j].load(wu + (size_t)col * width + c);
             }
-        } else {
-            for (int c = lane; c < width; c += 32) { ag = fmaf(xs[c], to_f32(g[c]), ag); au = fmaf(xs[c], to_f32(u[c]), au); }
+#pragma unroll
+            for (int j = 0; j < PAIR_CW; j++) {
+                float fg[N], fu[N]; vg[j].unpack(fg); vu[j].unpack(fu);
+#pragma unroll
+                for (int k = 0; k < N; k++) { ag[j] = fmaf(xs[c + k], fg[k], ag[j]); au[j] = fmaf(xs[c + k], fu[k], au[j]); }
+            }
         }
-        ag = warp_sum(ag); au = warp_sum(au);
-        if (lane == 0) act[(size_t)pair * ff + col] = from_f32<T>(ag / (1.0f + expf(-ag)) * au);
+    } else {
+        for (int c = lane; c < width; c += 32) {
+#pragma unroll
+            for (int j = 0; j < PAIR_CW; j++) {
+                const int col = min(col0 + j, ff - 1);
+                ag[j] = fmaf(xs[c], to_f32(wg[(size_t)col * width + c]), ag[j]);
+                au[j] = fmaf(xs[c], to_f32(wu[(size_t)col * width + c]), au[j]);
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < PAIR_CW; j++) {
+        const float g = warp_sum(ag[j]), u = warp_sum(au[j]);
+        if (lane == 0 && col0 + j < ff) act[(size_t)pair * ff + col0 + j] = from_f32<T>(g / (1.0f + expf(-g)) * u);
     }
 }
 
-// w_d: [experts, width, ff].  grid (tokens, column blocks).  shared: [tokens, width] or null.
-template <typename T>
+// w_d: [experts, width, ff].  grid (tokens, column blocks); a warp forms `cw` (1 or 2) columns.  The token's activations
+// lie in shared memory already multiplied by their experts' weights, so a column is ONE sum over all chosen experts'
+// rows (their loads in flight together) and one reduction.  shared: [tokens, width] or null.
+template <typename T, int CW>
 __global__ void __launch_bounds__(256) moe_pair_down_kernel(const T* act, const T* h, const int* ids, const float* weights,
                                                             const T* __restrict__ w_d, const T* shared, T* __restrict__ out,
-                                                            int width, int ff, int top, int experts, int cols_per_cta) {
-    extern __shared__ float xs[];                 // [top][ff] the token's activations, as floats
-    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+                                                            int width, int ff, int top, int experts) {
+    extern __shared__ float xs[];                 // [top][ff]: weight_k * activation of expert k (zeros for an identity expert)
+    __shared__ int id_s[MOE_MAX_TOP];
+    __shared__ float idw_s;                       // the identity experts' weights, summed
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     pdl_launch_dependents();
     pdl_wait(KID_MOE);
-    for (int k = 0; k < top; k++) {
-        const int e = ids[(size_t)t * top + k];
-        if (e < 0 || e >= experts) continue;
-        const T* ar = act + ((size_t)t * top + k) * ff;
-        for (int c = threadIdx.x; c < ff; c += blockDim.x) xs[k * ff + c] = to_f32(ar[c]);
+    if (threadIdx.x < 32) {
+        int e = -1; float w = 0.f;
+        if (lane < top) { e = ids[(size_t)t * top + lane]; w = weights[(size_t)t * top + lane]; }
+        const bool identity = lane < top && (e < 0 || e >= experts);
+        if (lane < top) id_s[lane] = identity ? -1 : e;
+        const float iw = warp_sum(identity ? w : 0.f);
+        if (lane == 0) idw_s = iw;
     }
     __syncthreads();
-    const int col0 = blockIdx.y * cols_per_cta;
-    const int col1 = min(width, col0 + cols_per_cta);
+    for (int i = threadIdx.x; i < top * ff; i += blockDim.x) {
+        const int k = i / ff;
+        xs[i] = id_s[k] < 0 ? 0.f : weights[(size_t)t * top + k] * to_f32(act[((size_t)t * top + k) * ff + i % ff]);
+    }
+    __syncthreads();
     constexpr int N = Vec16<T>::N;
     const bool vec = ff % N == 0;
-    for (int col = col0 + warp; col < col1; col += warps) {
-        float total = 0.f;
-        for (int k = 0; k < top; k++) {
-            const int e = ids[(size_t)t * top + k];
-            const float wk = weights[(size_t)t * top + k];
-            if (e < 0 || e >= experts) {           // identity: the input itself
-                total += wk * to_f32(h[(size_t)t * width + col]);
-                continue;
-            }
-            const T* d = w_d + ((size_t)e * width + col) * ff;
-            const float* x = xs + k * ff;
-            float acc = 0.f;
-            if (vec) {
+    const int col0 = (blockIdx.y * 8 + warp) * CW;
+    if (col0 >= width) return;
+    float acc[CW];
+#pragma unroll
+    for (int j = 0; j < CW; j++) acc[j] = 0.f;
+    if (vec) {
+        for (int c = lane * N; c < ff; c += 32 * N) {
 #pragma unroll 4
-                for (int c = lane * N; c < ff; c += 32 * N) {
-                    Vec16<T> vd; vd.load(d + c);
+            for (int k = 0; k < top; k++) {
+                const int e = id_s[k];
+                if (e < 0) continue;
+                const float* x = xs + k * ff + c;
+#pragma unroll
+                for (int j = 0; j < CW; j++) {
+                    const int col = min(col0 + j, width - 1);
+                    Vec16<T> vd; vd.load(w_d + ((size_t)e * width + col) * ff + c);
                     float fd[N]; vd.unpack(fd);
 #pragma unroll
-                    for (int j = 0; j < N; j++) acc = fmaf(x[c + j], fd[j], acc);
+                    for (int q = 0; q < N; q++) acc[j] = fmaf(x[q], fd[q], acc[j]);
                 }
-            } else {
-                for (int c = lane; c < ff; c += 32) acc = fmaf(x[c], to_f32(d[c]), acc);
             }
-            total += wk * warp_sum(acc);
         }
-        if (shared) total += to_f32(shared[(size_t)t * width + col]);
-        if (lane == 0) out[(size_t)t * width + col] = from_f32<T>(total);
+    } else {
+        for (int k = 0; k < top; k++) {
+            const int e = id_s[k];
+            if (e < 0) continue;
+#pragma unroll
+            for (int j = 0; j < CW; j++) {
+                const T* d = w_d + ((size_t)e * width + min(col0 + j, width - 1)) * ff;
+                for (int c = lane; c < ff; c += 32) acc[j] = fmaf(xs[k * ff + c], to_f32(d[c]), acc[j]);
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < CW; j++) {
+        float total = warp_sum(acc[j]);
+        const int col = col0 + j;
+        if (lane == 0 && col < width) {
+            if (idw_s != 0.f) total += idw_s * to_f32(h[(size_t)t * width + col]);      // identity experts: the input itself
+            if (shared) total += to_f32(shared[(size_t)t * width + col]);
+            out[(size_t)t * width + col] = from_f32<T>(total);
+        }
     }
 }
 
@@ -271,10 +329,8 @@ PLLM_EXPORT int pllm_moe_pair_glu(int dtype, const void* h, const int* ids, cons
     if (width <= 0 || ff <= 0 || top <= 0 || experts <= 0) return PLLM_ERR_SIZE;
     if ((size_t)width * sizeof(float) > 48 * 1024) return PLLM_ERR_LIMIT;
     PLLM_DISPATCH_DTYPE(dtype, {
-        // a warp a column while the pairs are few (every SM gets CTAs), more columns a CTA as they grow
-        const int cols = n_tokens * top <= 64 ? 8 : 32;
-        launch_chained(moe_pair_glu_kernel<T>, dim3(n_tokens * top, (ff + cols - 1) / cols), dim3(256), (size_t)width * sizeof(float),
-                       stream, (const T*)h, ids, (const T*)w_gu, (T*)act, width, ff, top, experts, cols);
+        launch_chained(moe_pair_glu_kernel<T>, dim3(n_tokens * top, (ff + 8 * PAIR_CW - 1) / (8 * PAIR_CW)), dim3(256),
+                       (size_t)width * sizeof(float), stream, (const T*)h, ids, (const T*)w_gu, (T*)act, width, ff, top, experts);
     });
     return launch_status();
 }
@@ -284,12 +340,18 @@ PLLM_EXPORT int pllm_moe_pair_down(int dtype, const void* act, const void* h, co
                                    cudaStream_t stream) {
     if (n_tokens <= 0) return PLLM_OK;
     if (width <= 0 || ff <= 0 || top <= 0 || experts <= 0) return PLLM_ERR_SIZE;
+    if (top > MOE_MAX_TOP) return PLLM_ERR_LIMIT;
     if ((size_t)top * ff * sizeof(float) > 48 * 1024) return PLLM_ERR_LIMIT;
     PLLM_DISPATCH_DTYPE(dtype, {
-        const int cols = n_tokens <= 64 ? 8 : 32;
-        launch_chained(moe_pair_down_kernel<T>, dim3(n_tokens, (width + cols - 1) / cols), dim3(256),
-                       (size_t)top * ff * sizeof(float), stream, (const T*)act, (const T*)h, ids, weights, (const T*)w_d,
-                       (const T*)shared, (T*)out, width, ff, top, experts, cols);
+        // a column a warp while the tokens are few (every SM gets CTAs), two from a handful of tokens on
+        if (n_tokens <= 4)
+            launch_chained(moe_pair_down_kernel<T, 1>, dim3(n_tokens, (width + 7) / 8), dim3(256), (size_t)top * ff * sizeof(float),
+                           stream, (const T*)act, (const T*)h, ids, weights, (const T*)w_d, (const T*)shared, (T*)out, width, ff, top,
+                           experts);
+        else
+            launch_chained(moe_pair_down_kernel<T, 2>, dim3(n_tokens, (width + 15) / 16), dim3(256), (size_t)top * ff * sizeof(float),
+                           stream, (const T*)act, (const T*)h, ids, weights, (const T*)w_d, (const T*)shared, (T*)out, width, ff, top,
+                           experts);
     });
     return launch_status();
 }
