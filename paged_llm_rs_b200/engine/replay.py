@@ -15,7 +15,7 @@ For a step in which something is wanted, ``<out>/<step>.f32`` receives the logit
 at the wanted places as little-endian float32 [wanted, vocab].  After every
 step a line ``done <step>`` is printed and flushed.
 
-Beyond that contract, for the tests: ``--page-size`` (a divisor of 64),
+Beyond that, for the tests: ``--page-size`` (a divisor of 64),
 ``--prefix-cache on`` (a request's first entry claims the pages that already hold
 its leading tokens, as the scheduler's admission does, crates/pagedllm/src/scheduler.rs:596-621,
 and pages are named when a step is committed) and ``--graphs on`` (steps run as
