@@ -327,8 +327,9 @@ PLLM_EXPORT int pllm_moe_pair_glu(int dtype, const void* h, const int* ids, cons
                                   int ff, int top, int experts, cudaStream_t stream) {
     if (n_tokens <= 0) return PLLM_OK;
     if (width <= 0 || ff <= 0 || top <= 0 || experts <= 0) return PLLM_ERR_SIZE;
-    if ((size_t)width * sizeof(float) > 48 * 1024) return PLLM_ERR_LIMIT;
+    if ((size_t)width * sizeof(float) > 200 * 1024) return PLLM_ERR_LIMIT;
     PLLM_DISPATCH_DTYPE(dtype, {
+        cudaFuncSetAttribute(moe_pair_glu_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((size_t)width * sizeof(float)));
         launch_chained(moe_pair_glu_kernel<T>, dim3(n_tokens * top, (ff + 8 * PAIR_CW - 1) / (8 * PAIR_CW)), dim3(256),
                        (size_t)width * sizeof(float), stream, (const T*)h, ids, (const T*)w_gu, (T*)act, width, ff, top, experts);
     });
@@ -341,8 +342,10 @@ PLLM_EXPORT int pllm_moe_pair_down(int dtype, const void* act, const void* h, co
     if (n_tokens <= 0) return PLLM_OK;
     if (width <= 0 || ff <= 0 || top <= 0 || experts <= 0) return PLLM_ERR_SIZE;
     if (top > MOE_MAX_TOP) return PLLM_ERR_LIMIT;
-    if ((size_t)top * ff * sizeof(float) > 48 * 1024) return PLLM_ERR_LIMIT;
+    if ((size_t)top * ff * sizeof(float) > 200 * 1024) return PLLM_ERR_LIMIT;
     PLLM_DISPATCH_DTYPE(dtype, {
+        cudaFuncSetAttribute(moe_pair_down_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((size_t)top * ff * sizeof(float)));
+        cudaFuncSetAttribute(moe_pair_down_kernel<T, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((size_t)top * ff * sizeof(float)));
         // a column a warp while the tokens are few (every SM gets CTAs), two from a handful of tokens on
         if (n_tokens <= 4)
             launch_chained(moe_pair_down_kernel<T, 1>, dim3(n_tokens, (width + 7) / 8), dim3(256), (size_t)top * ff * sizeof(float),
