@@ -23,12 +23,21 @@ the mixer.  Sizes, the scale and the norms' eps are parameters.
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..errors import KernelError
 from ..kernels import ops
 from .base import Mixer, PlanWish, RowNeed, register_mixer
 from .spec import TensorSpec
+
+
+# For the few rows of a decode step in bfloat16 the per-head products are folded into their neighbours ahead of time:
+# q~ = (W_uk^T W_uq) c_q and out = (W_o W_uv) o~, each ONE weight-streaming product instead of a product and a batched
+# product: two launches fewer a layer, at heads x kv_rank x (q_rank + width) further weights (formed in float32, rounded
+# once).  Prompt portions keep the unfolded products, which cost fewer multiplications.  PAGED_LLM_LATENT_FOLD=0: never.
+FOLD_FOR_FEW_ROWS = os.environ.get("PAGED_LLM_LATENT_FOLD", "1") != "0"
 
 
 class LatentAttention(Mixer):
@@ -45,6 +54,7 @@ class LatentAttention(Mixer):
         self.names = dict(dq="dq", dq_norm="dq.norm", uq="uq", dkv="dkv", dkv_norm="dkv.norm", uk="uk", uv="uv", o="o")
         self.names.update(p.get("names", {}))
         self.w_down = self.w_uq = self.w_uk = self.w_uv = self.w_o = self.g_q = self.g_kv = None
+        self.w_quk = self.w_ov = None          # the folded weights of decode steps (bfloat16 only)
         self._need = None
 
     def tensors(self):
@@ -64,6 +74,11 @@ class LatentAttention(Mixer):
         self.g_q, self.g_kv = t("dq_norm"), t("dkv_norm")
         self.w_uk = t("uk").view(H, self.dim, self.kv_rank)                   # q~_a = q_a W_uk,a       [dim] x [dim, kv_rank]
         self.w_uv = t("uv").view(H, self.vdim, self.kv_rank).transpose(1, 2).contiguous()   # o_a = o~_a W_uv,a^T  [kv_rank, vdim]
+        if FOLD_FOR_FEW_ROWS and self.rt.dtype == torch.bfloat16:
+            uk, uq = self.w_uk.float(), self.w_uq.view(H, self.dim, self.q_rank).float()
+            self.w_quk = torch.einsum("hdr,hdq->hrq", uk, uq).reshape(H * self.kv_rank, self.q_rank).to(self.rt.dtype).contiguous()
+            o, uv = self.w_o.view(self.hidden, H, self.vdim).float(), t("uv").view(H, self.vdim, self.kv_rank).float()
+            self.w_ov = torch.einsum("whv,hvr->whr", o, uv).reshape(self.hidden, H * self.kv_rank).to(self.rt.dtype).contiguous()
 
     def cache_need(self):
         if self._need is None:
@@ -83,6 +98,11 @@ class LatentAttention(Mixer):
         cq = torch.empty((T, self.q_rank), dtype=x.dtype, device=x.device)
         ops.latent_norm_write(qa, self.g_q, self.g_kv, self.eps, cq, rows if writes_cache else None, g.slots,
                               self.q_rank, R, st)
+        if self.w_quk is not None and T <= ops.SKINNY_MAX_M:
+            q_lat = ops.linear(cq, self.w_quk, status=st).view(T, H, R)
+            o_lat = torch.empty_like(q_lat)
+            ops.latent_attention(q_lat, rows, g.block_tables, g.plan, o_lat, self.scale, st)
+            return ops.linear(o_lat.view(T, H * R), self.w_ov, status=st)
         q = ops.linear(cq, self.w_uq, status=st)
         # per head, batched over views [H, T, .] of tensors laid out [T, H, .] (what the attention kernel reads and writes)
         q_lat = torch.empty((T, H, R), dtype=x.dtype, device=x.device)
