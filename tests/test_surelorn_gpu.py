@@ -484,3 +484,67 @@ def test_trace_replay_and_command_line(models, tmp_path):
     for tok in out:
         assert tok == P.greedy(P.forward(cfg, w, seq)[-1])
         seq = seq + [tok]
+
+
+# ------------------------------------------------------------------------ configurations drawn at random
+
+def random_configuration(seed):
+    """Sizes, counts, layer order and constants drawn from a seed: heads from 1 to 24, latent widths with and without the
+    tensor-core kernels' sizes, routers with and without groups, identity experts, shared experts, layers without a
+    feed-forward and layers that run earlier layers' tensors."""
+    import random
+    from surelorn_models import dense, layer, mixer, moe
+    rnd = random.Random(seed)
+    width = rnd.choice([48, 64, 96, 128, 256])
+
+    def a_mixer():
+        return mixer(rnd.choice([1, 2, 3, 4, 6, 8, 12, 16, 24]), rnd.choice([8, 16, 24, 32, 64]), rnd.choice([8, 16, 40, 64]),
+                     rnd.choice([16, 24, 40, 64, 96, 128, 256]), rnd.choice([8, 24, 32, 80]), scale=rnd.choice([0.1, 0.25, 0.5]))
+
+    def a_mlp():
+        kind = rnd.choice(["dense", "moe", "moe", None])
+        if kind == "dense":
+            return dense(rnd.choice([32, 72, 128, 192]))
+        if kind is None:
+            return None
+        count = rnd.choice([1, 2, 4])
+        per = rnd.choice([1, 2, 3])
+        total = count * per
+        identity = rnd.choice([0, 0, 1, min(2, total - 1)])
+        keep = rnd.randint(1, count)
+        top = rnd.randint(1, min(keep * per, 4))
+        return moe(total - identity, top, rnd.choice([24, 64, 128]), identity=identity,
+                   groups=(count, keep) if rnd.random() < 0.8 else None, shared=rnd.choice([None, 32, 64, 128]))
+    layers = []
+    for i in range(rnd.randint(2, 5)):
+        lenders = [j for j, L in enumerate(layers) if L.get("weights_of") is None]
+        if lenders and rnd.random() < 0.3:
+            j = rnd.choice(lenders)
+            layers.append(layer(layers[j]["mixer"], layers[j]["mlp"], weights_of=j))
+        else:
+            layers.append(layer(a_mixer(), a_mlp()))
+    for L in layers:      # a router without groups has no `groups` key; `top` must fit what can be chosen
+        m = L["mlp"]
+        if m and m["kind"] == "moe" and "groups" not in m["router"]:
+            m["router"]["top"] = min(m["router"]["top"], m["router"]["experts"] + m["router"]["identity"])
+    return dict(architecture="Surelorn", vocab=rnd.choice([97, 256, 640]), width=width,
+                embedding=dict(scale=rnd.choice([1.0, 4.0, 16.0])), norm=dict(eps=rnd.choice([1e-5, 1e-6])), layers=layers)
+
+
+@pytest.mark.parametrize("seed", list(range(1, 13)))
+def test_configurations_drawn_at_random(tmp_path, seed):
+    cfg = random_configuration(seed)
+    folder, cfg, w = write_model(tmp_path, f"random{seed}", seed=seed, cfg=cfg)
+    toks = tokens_for(cfg, 130, seed)
+    want = P.forward(cfg, w, toks)
+    for dtype in DTYPES:
+        s = Served(folder, dtype, page=16, pages=24)
+        whole = s.step([("w", toks, list(range(130)))])
+        s.end("w")
+        outs, at = [], 0
+        for c in [50, 2, 47, 1, 1, 19, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1]:
+            outs.append(s.step([("c", toks[at:at + c], list(range(c)))]))
+            at += c
+        assert at == 130
+        assert agrees(whole, want, dtype), (seed, dtype, cfg)
+        assert agrees(torch.cat(outs), want, dtype), (seed, dtype, cfg)
