@@ -1,4 +1,5 @@
-// A mixture of gated feed-forward experts: the router, and the experts for a few rows.
+// A mixture of gated feed-forward experts: the router, the experts for a few rows, and what surrounds the
+// grouped tensor-core products for many rows (sorting the pairs by expert, gathering, combining).
 //
 // Router (all float): z = W_r h over every router output (experts with tensors first, identity
 // experts last); s = softmax(z); choice = s + correction.  Outputs form `groups` equal groups of
@@ -8,7 +9,7 @@
 // the lower index.
 //
 // Experts, the weight-streaming form: a (token, chosen expert) pair is a row of its own; a warp
-// forms one output column at a time from that expert's weight rows, so every weight row that a step
+// forms a few output columns at a time from that expert's weight rows, so every weight row that a step
 // touches is read once per pair from L2 / HBM and nothing is read for experts that nobody chose.
 //   pair_glu:   act[pair, :] = silu(Wg_e h) * (Wu_e h)
 //   pair_down:  out[t, :] = sum_k w[t, k] * (Wd_e act[pair]  |  h[t] for an identity expert) (+ shared[t, :])
