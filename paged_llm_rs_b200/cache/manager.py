@@ -6,7 +6,8 @@ sequence and no state slots (crates/pagedllm/src/batch.rs:279-315,
 crates/pagedllm/src/blocks.rs:296-430).  Here layers whose mixers ask for the
 same kind of cache (all keys, or a window of them; the same kv heads and head
 size) form a group with pages, an allocator and tables of its own; a window
-group gives pages back as soon as the window has passed them.  Mixers that ask
+group gives pages back as soon as the window has passed them, but for the pages
+of the first tokens that its mixers keep seeing (``keep_first``).  Mixers that ask
 for a ``StateNeed`` get a slot of fixed size per request instead.
 
 One page holds ``page_size`` tokens of every layer of its group.  How a page
@@ -86,6 +87,12 @@ class CacheGroup:
     @property
     def window(self) -> Optional[int]:
         return self.need.window if self.need.kind == "window" else None
+
+    @property
+    def kept_pages(self) -> int:
+        """Leading pages of a request that a window group never gives back: those that hold its first
+        ``keep_first`` tokens."""
+        return -(-int(getattr(self.need, "keep_first", 0) or 0) // self.page_size)
 
 
 @dataclass
@@ -215,7 +222,7 @@ class CacheManager:
                 n = -(-tokens // self.page_size)
             else:
                 span = min(tokens, g.window + (step_tokens or tokens))
-                n = min(-(-tokens // self.page_size), -(-span // self.page_size) + 1)
+                n = min(-(-tokens // self.page_size), -(-span // self.page_size) + 1 + g.kept_pages)
             most = max(most, n)
         return most
 
@@ -311,7 +318,7 @@ class CacheManager:
                 first_needed = max(0, t.tokens - g.window + 1)
                 while (t.first_live + 1) * self.page_size <= first_needed:
                     b = t.blocks[t.first_live]
-                    if b >= 0:
+                    if b >= 0 and t.first_live >= g.kept_pages:      # (the pages of the kept first tokens stay)
                         g.allocator.release(b)
                         t.blocks[t.first_live] = FREED
                     t.first_live += 1

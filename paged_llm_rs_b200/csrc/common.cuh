@@ -32,6 +32,21 @@ template <typename T> __device__ __forceinline__ T from_f32(float x);
 template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
 template <> __device__ __forceinline__ bf16 from_f32<bf16>(float x) { return __float2bfloat16_rn(x); }
 
+// The gated activations y = act(g, u) of the feed-forwards, g the gate's product and u the up product:
+//   GLU_SILU     silu(g) * u
+//   GLU_RELU     max(g, 0) * u
+//   GLU_CLAMPED  g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit)
+enum : int { GLU_SILU = 0, GLU_RELU = 1, GLU_CLAMPED = 2 };
+__device__ __forceinline__ float glu_act(int kind, float limit, float g, float u) {
+    if (kind == GLU_RELU) return fmaxf(g, 0.f) * u;
+    if (kind == GLU_CLAMPED) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+    }
+    return g / (1.0f + expf(-g)) * u;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -313,7 +313,7 @@ PLLM_EXPORT int pllm_rmsnorm(int dtype, const void* x, const void* delta, void* 
 // out[n, inter] = silu(gate) * up, silu(z) = z / (1 + exp(-z)).
 template <typename T>
 __global__ void swiglu_kernel(const T* in, T* __restrict__ out, int inter, long long total_vec,
-                              int vec_per_row) {
+                              int vec_per_row, int act, float limit) {
     constexpr int N = Vec16<T>::N;
     pdl_launch_dependents();
     pdl_wait(KID_SWIGLU);
@@ -326,12 +326,12 @@ __global__ void swiglu_kernel(const T* in, T* __restrict__ out, int inter, long 
         float fg[N], fu[N];
         vg.unpack(fg); vu.unpack(fu);
 #pragma unroll
-        for (int k = 0; k < N; k++) fg[k] = fg[k] / (1.0f + expf(-fg[k])) * fu[k];
+        for (int k = 0; k < N; k++) fg[k] = glu_act(act, limit, fg[k], fu[k]);
         Vec16<T> o; o.pack(fg); o.store(out + row * inter + c);
     }
 }
 template <typename T>
-__global__ void swiglu_scalar_kernel(const T* in, T* __restrict__ out, int inter, long long total) {
+__global__ void swiglu_scalar_kernel(const T* in, T* __restrict__ out, int inter, long long total, int act, float limit) {
     pdl_launch_dependents();
     pdl_wait(KID_SWIGLU);
     for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
@@ -339,12 +339,14 @@ __global__ void swiglu_scalar_kernel(const T* in, T* __restrict__ out, int inter
         const long long row = idx / inter;
         const int c = (int)(idx % inter);
         const float g = to_f32(in[row * 2 * inter + c]), u = to_f32(in[row * 2 * inter + inter + c]);
-        out[idx] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+        out[idx] = from_f32<T>(glu_act(act, limit, g, u));
     }
 }
 
-PLLM_EXPORT int pllm_swiglu(int dtype, const void* in, void* out, int n_rows, int inter, cudaStream_t stream) {
+// (act: one of GLU_SILU, GLU_RELU, GLU_CLAMPED with its limit; see common.cuh)
+PLLM_EXPORT int pllm_swiglu(int dtype, const void* in, void* out, int n_rows, int inter, int act, float limit, cudaStream_t stream) {
     if (n_rows <= 0) return PLLM_OK;
+    if (act < GLU_SILU || act > GLU_CLAMPED) return PLLM_ERR_SIZE;
     if (inter <= 0) return PLLM_ERR_SIZE;
     PLLM_DISPATCH_DTYPE(dtype, {
         constexpr int N = Vec16<T>::N;
@@ -352,12 +354,12 @@ PLLM_EXPORT int pllm_swiglu(int dtype, const void* in, void* out, int n_rows, in
             long long total = (long long)n_rows * (inter / N);
             int blocks = (int)min((long long)sm_count() * 16, (total + 255) / 256);
             launch_chained(swiglu_kernel<T>, dim3(blocks), dim3(256), 0, stream, (const T*)in, (T*)out, inter, total,
-                           inter / N);
+                           inter / N, act, limit);
         } else {
             long long total = (long long)n_rows * inter;
             int blocks = (int)min((long long)sm_count() * 16, (total + 255) / 256);
             launch_chained(swiglu_scalar_kernel<T>, dim3(blocks), dim3(256), 0, stream, (const T*)in, (T*)out, inter,
-                           total);
+                           total, act, limit);
         }
     });
     return launch_status();

@@ -38,13 +38,22 @@ constexpr int G_THREADS = 192;
 
 }  // namespace
 
+// The gated activations other than silu (common.cuh), with the fast exponential and division as the silu above.
+__device__ __forceinline__ float glu_act_fast(int kind, float limit, float g, float u) {
+    if (kind == GLU_RELU) return fmaxf(g, 0.f) * u;
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return __fdividef(g, 1.0f + __expf(-1.702f * g)) * (u + 1.0f);
+}
+
 // map_a: x [M, K], box 64 x 128.  map_b: W [rows, K], box 64 x BN (plain) or 64 x BN/2 (GLU).
 // y: [M, n_out] bfloat16; n_out = N (plain) or N / 2 (GLU, W = [gate; up] of n_out rows each).
 template <int EPI, int BN>
 __global__ void __launch_bounds__(G_THREADS, 1) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                     const __grid_constant__ CUtensorMap map_b,
                                                                     bf16* __restrict__ y, int M, int n_out, int K,
-                                                                    int* status, const int* tile_expert, int expert_rows) {
+                                                                    int* status, const int* tile_expert, int expert_rows,
+                                                                    int act, float limit) {
     // Grouped form (tile_expert given): the rows of x are sorted by expert, every expert's rows padded to whole
     // tiles of 128; tile_expert[m tile] names the expert whose weights that tile multiplies (its rows of W start at
     // expert * expert_rows), or is negative for a tile past the last one in use, which every role skips alike.
@@ -174,7 +183,8 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tcgen05_kernel(const __grid
                         const float u0 = round_bf16(__uint_as_float(u[2 * k])), u1 = round_bf16(__uint_as_float(u[2 * k + 1]));
                         // (fast exponential and division: their error is far below the rounding to bfloat16,
                         //  and the epilogue must keep pace with the tensor cores)
-                        out[k] = pack2(__fdividef(g0, 1.0f + __expf(-g0)) * u0, __fdividef(g1, 1.0f + __expf(-g1)) * u1);
+                        if (act == GLU_SILU) out[k] = pack2(__fdividef(g0, 1.0f + __expf(-g0)) * u0, __fdividef(g1, 1.0f + __expf(-g1)) * u1);
+                        else out[k] = pack2(glu_act_fast(act, limit, g0, u0), glu_act_fast(act, limit, g1, u1));
                     }
                 } else {
                     tmem_wait_ld();
@@ -219,7 +229,7 @@ namespace {
 
 template <int EPI, int BN>
 int launch_gemm(const void* x, const void* w, void* y, int M, int n_out, int K, int* status,
-                cudaStream_t stream, const int* tile_expert = nullptr, int n_experts = 1) {
+                cudaStream_t stream, const int* tile_expert = nullptr, int n_experts = 1, int act = GLU_SILU, float limit = 0.f) {
     constexpr bool GLU = EPI == 1;
     constexpr int OUT_BN = GLU ? BN / 2 : BN;
     constexpr int STAGE = G_TILE_A + BN * G_BK * 2, STAGES = G_SMEM_TILES / STAGE;
@@ -236,40 +246,44 @@ int launch_gemm(const void* x, const void* w, void* y, int M, int n_out, int K, 
     const dim3 grid(n_tiles < g_sm_count ? n_tiles : g_sm_count);
     cudaFuncSetAttribute(gemm_tcgen05_kernel<EPI, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_chained(gemm_tcgen05_kernel<EPI, BN>, grid, dim3(G_THREADS), smem, stream, map_a, map_b, (bf16*)y, M, n_out, K, status,
-                   tile_expert, GLU ? 2 * n_out : n_out);
+                   tile_expert, GLU ? 2 * n_out : n_out, act, limit);
     return launch_status();
 }
 
 }  // namespace
 
 // x: [M, K]; w: [n_out, K], or with glu [2 n_out, K] = gate rows then up rows; y: [M, n_out]; all bfloat16.
-PLLM_EXPORT int pllm_gemm_tcgen05(const void* x, const void* w, void* y, int M, int n_out, int K, int glu, int* status,
+// glu: 0 a plain product, else 1 + the gated activation's kind (common.cuh), with its limit.
+PLLM_EXPORT int pllm_gemm_tcgen05(const void* x, const void* w, void* y, int M, int n_out, int K, int glu, float limit, int* status,
                                   cudaStream_t stream) {
-    if (!pllm_gemm_tcgen05_supports(M, n_out, K, glu)) return PLLM_ERR_SIZE;
+    if (!pllm_gemm_tcgen05_supports(M, n_out, K, glu) || glu < 0 || glu > 1 + GLU_CLAMPED) return PLLM_ERR_SIZE;
+    const int act = glu ? glu - 1 : GLU_SILU;
     if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15) return PLLM_ERR_ALIGN;
     // tiles of 256 columns of W where the width divides into them and they still give every SM one
     const int tiles_m = (M + G_BM - 1) / G_BM;
     const int unit = glu ? 128 : 256;
     const bool wide = n_out % unit == 0 && (long long)tiles_m * (n_out / unit) >= sm_count();
     if (glu)
-        return wide ? launch_gemm<1, 256>(x, w, y, M, n_out, K, status, stream)
-                    : launch_gemm<1, 128>(x, w, y, M, n_out, K, status, stream);
+        return wide ? launch_gemm<1, 256>(x, w, y, M, n_out, K, status, stream, nullptr, 1, act, limit)
+                    : launch_gemm<1, 128>(x, w, y, M, n_out, K, status, stream, nullptr, 1, act, limit);
     return wide ? launch_gemm<0, 256>(x, w, y, M, n_out, K, status, stream)
                 : launch_gemm<0, 128>(x, w, y, M, n_out, K, status, stream);
 }
 
 // The grouped form: x [M, K] holds the rows sorted by expert, each expert's rows padded to whole tiles of 128
 // (M a multiple of 128, an upper bound); w [experts, n_out (glu: 2 n_out), K]; tile_expert [M / 128] on the device.
-PLLM_EXPORT int pllm_gemm_tcgen05_grouped(const void* x, const void* w, void* y, int M, int n_out, int K, int glu,
+PLLM_EXPORT int pllm_gemm_tcgen05_grouped(const void* x, const void* w, void* y, int M, int n_out, int K, int glu, float limit,
                                           const int* tile_expert, int n_experts, int* status, cudaStream_t stream) {
     if (!pllm_gemm_tcgen05_supports(M, n_out, K, glu) || M % G_BM || n_experts < 1 || !tile_expert) return PLLM_ERR_SIZE;
+    if (glu < 0 || glu > 1 + GLU_CLAMPED) return PLLM_ERR_SIZE;
+    const int act = glu ? glu - 1 : GLU_SILU;
     if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15) return PLLM_ERR_ALIGN;
     const int tiles_m = M / G_BM;
     const int unit = glu ? 128 : 256;
     const bool wide = n_out % unit == 0 && (long long)tiles_m * (n_out / unit) >= sm_count();
     if (glu)
-        return wide ? launch_gemm<1, 256>(x, w, y, M, n_out, K, status, stream, tile_expert, n_experts)
-                    : launch_gemm<1, 128>(x, w, y, M, n_out, K, status, stream, tile_expert, n_experts);
+        return wide ? launch_gemm<1, 256>(x, w, y, M, n_out, K, status, stream, tile_expert, n_experts, act, limit)
+                    : launch_gemm<1, 128>(x, w, y, M, n_out, K, status, stream, tile_expert, n_experts, act, limit);
     return wide ? launch_gemm<0, 256>(x, w, y, M, n_out, K, status, stream, tile_expert, n_experts)
                 : launch_gemm<0, 128>(x, w, y, M, n_out, K, status, stream, tile_expert, n_experts);
 }

@@ -6,13 +6,16 @@
 // neighbours; a group's score is its largest choice score, and only outputs of the `keep` best groups
 // can be chosen (the others count as minus infinity).  The `top` largest choice scores are chosen; a
 // chosen output's weight is its s divided by the sum of the chosen s (+ 1e-20).  Equal scores go to
-// the lower index.
+// the lower index.  A bias (one float a router output) may be added to z; with a bias and no correction the weights
+// are the softmax over the chosen logits alone, whatever their size among all.  The router's matrix may carry `extra`
+// further rows behind its outputs, whose products with h leave as they are (a gate of the shared expert, say).
 //
 // Experts, the weight-streaming form: a (token, chosen expert) pair is a row of its own; a warp
 // forms a few output columns at a time from that expert's weight rows, so every weight row that a step
 // touches is read once per pair from L2 / HBM and nothing is read for experts that nobody chose.
-//   pair_glu:   act[pair, :] = silu(Wg_e h) * (Wu_e h)
-//   pair_down:  out[t, :] = sum_k w[t, k] * (Wd_e act[pair]  |  h[t] for an identity expert) (+ shared[t, :])
+//   pair_glu:   act[pair, :] = glu(Wg_e h, Wu_e h)     (silu(g) * u, or another gated activation of common.cuh)
+//   pair_down:  out[t, :] = sum_k w[t, k] * (Wd_e act[pair]  |  h[t] for an identity expert) (+ shared[t, :], times
+//               sigmoid(shared_gate[t]) when the shared expert is gated)
 // The right form for the few tokens of a decode step and for the float32 engine; many rows in bfloat16
 // go to the grouped tensor-core product instead.
 #include "common.cuh"
@@ -40,13 +43,14 @@ template <typename T, int TOK>
 __global__ void __launch_bounds__(256) moe_route_kernel(const T* h, const float* __restrict__ w_router,
                                                         const float* __restrict__ correction, int* __restrict__ ids,
                                                         float* __restrict__ weights, int n_tokens, int width, int outputs,
-                                                        int top, int groups, int keep) {
+                                                        int top, int groups, int keep, const float* __restrict__ bias, int extra,
+                                                        float* __restrict__ extra_out) {
     extern __shared__ float smem[];      // xs[TOK][width]; per token: s[outputs], choice[outputs], gscore[groups]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int t0 = blockIdx.x * TOK;
     float* xs = smem;
     float* per_token = xs + (size_t)TOK * width;
-    const int per = 2 * outputs + groups;
+    const int per = 2 * outputs + groups + extra;
     pdl_launch_dependents();
     pdl_wait(KID_MOE);
     constexpr int N = Vec16<T>::N;
@@ -66,7 +70,7 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const T* h, const float*
         }
     }
     __syncthreads();
-    for (int e = warp; e < outputs; e += 8) {
+    for (int e = warp; e < outputs + extra; e += 8) {
         const float* wr = w_router + (size_t)e * width;
         float acc[TOK];
 #pragma unroll
@@ -91,7 +95,10 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const T* h, const float*
 #pragma unroll
         for (int k = 0; k < TOK; k++) {
             const float z = warp_sum(acc[k]);
-            if (lane == 0) per_token[k * per + e] = z;
+            if (lane == 0) {
+                if (e < outputs) per_token[k * per + e] = z + (bias ? bias[e] : 0.f);
+                else per_token[k * per + 2 * outputs + groups + (e - outputs)] = z;
+            }
         }
     }
     __syncthreads();
@@ -101,6 +108,7 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const T* h, const float*
         float* s = per_token + k * per;
         float* choice = s + outputs;
         float* gscore = choice + outputs;
+        if (lane < extra) extra_out[(size_t)t * extra + lane] = gscore[groups + lane];
         float zmax = -CUDART_INF_F;
         for (int e = lane; e < outputs; e += 32) zmax = fmaxf(zmax, s[e]);
         zmax = warp_max(zmax);
@@ -165,24 +173,28 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const T* h, const float*
 
 template <typename T, int TOK>
 static void launch_route(const void* h, const float* w_router, const float* correction, int* ids, float* weights, int n_tokens,
-                         int width, int outputs, int top, int groups, int keep, cudaStream_t stream) {
-    const size_t smem = ((size_t)TOK * width + (size_t)TOK * (2 * outputs + groups)) * sizeof(float);
+                         int width, int outputs, int top, int groups, int keep, const float* bias, int extra, float* extra_out,
+                         cudaStream_t stream) {
+    const size_t smem = ((size_t)TOK * width + (size_t)TOK * (2 * outputs + groups + extra)) * sizeof(float);
     cudaFuncSetAttribute(moe_route_kernel<T, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_chained(moe_route_kernel<T, TOK>, dim3((n_tokens + TOK - 1) / TOK), dim3(256), smem, stream, (const T*)h, w_router,
-                   correction, ids, weights, n_tokens, width, outputs, top, groups, keep);
+                   correction, ids, weights, n_tokens, width, outputs, top, groups, keep, bias, extra, extra_out);
 }
 
+// bias: [outputs] or null.  extra (<= 32): rows of w_router behind the outputs; extra_out [tokens, extra] receives their products.
 PLLM_EXPORT int pllm_moe_route(int dtype, const void* h, const float* w_router, const float* correction, int* ids, float* weights,
-                               int n_tokens, int width, int outputs, int top, int groups, int keep, cudaStream_t stream) {
+                               int n_tokens, int width, int outputs, int top, int groups, int keep, const float* bias, int extra,
+                               float* extra_out, cudaStream_t stream) {
     if (n_tokens <= 0) return PLLM_OK;
+    if (extra < 0 || extra > 32 || (extra > 0 && !extra_out)) return PLLM_ERR_SIZE;
     if (width <= 0 || outputs <= 0 || top <= 0 || groups <= 0 || keep <= 0 || outputs % groups || keep > groups) return PLLM_ERR_SIZE;
     if (outputs > MOE_MAX_OUTPUTS || top > MOE_MAX_TOP || top > outputs) return PLLM_ERR_LIMIT;
     // eight tokens a CTA from some hundreds of tokens on (a router row is then read once for the eight), where they fit
-    const bool many = n_tokens >= 256 && (8 * (size_t)width + 8 * (size_t)(2 * outputs + groups)) * sizeof(float) <= 160 * 1024;
-    if (((size_t)width + 2 * outputs + groups) * sizeof(float) > 200 * 1024) return PLLM_ERR_LIMIT;
+    const bool many = n_tokens >= 256 && (8 * (size_t)width + 8 * (size_t)(2 * outputs + groups + extra)) * sizeof(float) <= 160 * 1024;
+    if (((size_t)width + 2 * outputs + groups + extra) * sizeof(float) > 200 * 1024) return PLLM_ERR_LIMIT;
     PLLM_DISPATCH_DTYPE(dtype, {
-        if (many) launch_route<T, 8>(h, w_router, correction, ids, weights, n_tokens, width, outputs, top, groups, keep, stream);
-        else launch_route<T, 1>(h, w_router, correction, ids, weights, n_tokens, width, outputs, top, groups, keep, stream);
+        if (many) launch_route<T, 8>(h, w_router, correction, ids, weights, n_tokens, width, outputs, top, groups, keep, bias, extra, extra_out, stream);
+        else launch_route<T, 1>(h, w_router, correction, ids, weights, n_tokens, width, outputs, top, groups, keep, bias, extra, extra_out, stream);
     });
     return launch_status();
 }
@@ -194,7 +206,7 @@ PLLM_EXPORT int pllm_moe_route(int dtype, const void* h, const float* w_router, 
 #define PAIR_CW 4
 template <typename T>
 __global__ void __launch_bounds__(256) moe_pair_glu_kernel(const T* h, const int* ids, const T* __restrict__ w_gu, T* __restrict__ act,
-                                                           int width, int ff, int top, int experts) {
+                                                           int width, int ff, int top, int experts, int glu, float limit) {
     extern __shared__ float xs[];
     const int pair = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     pdl_launch_dependents();
@@ -246,7 +258,7 @@ __global__ void __launch_bounds__(256) moe_pair_glu_kernel(const T* h, const int
 #pragma unroll
     for (int j = 0; j < PAIR_CW; j++) {
         const float g = warp_sum(ag[j]), u = warp_sum(au[j]);
-        if (lane == 0 && col0 + j < ff) act[(size_t)pair * ff + col0 + j] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+        if (lane == 0 && col0 + j < ff) act[(size_t)pair * ff + col0 + j] = from_f32<T>(glu_act(glu, limit, g, u));
     }
 }
 
@@ -256,7 +268,7 @@ __global__ void __launch_bounds__(256) moe_pair_glu_kernel(const T* h, const int
 template <typename T, int CW>
 __global__ void __launch_bounds__(256) moe_pair_down_kernel(const T* act, const T* h, const int* ids, const float* weights,
                                                             const T* __restrict__ w_d, const T* shared, T* __restrict__ out,
-                                                            int width, int ff, int top, int experts) {
+                                                            int width, int ff, int top, int experts, const float* shared_gate) {
     extern __shared__ float xs[];                 // [top][ff]: weight_k * activation of expert k (zeros for an identity expert)
     __shared__ int id_s[MOE_MAX_TOP];
     __shared__ float idw_s;                       // the identity experts' weights, summed
@@ -318,28 +330,29 @@ __global__ void __launch_bounds__(256) moe_pair_down_kernel(const T* act, const 
         const int col = col0 + j;
         if (lane == 0 && col < width) {
             if (idw_s != 0.f) total += idw_s * to_f32(h[(size_t)t * width + col]);      // identity experts: the input itself
-            if (shared) total += to_f32(shared[(size_t)t * width + col]);
+            if (shared) total += to_f32(shared[(size_t)t * width + col]) * (shared_gate ? 1.0f / (1.0f + expf(-shared_gate[t])) : 1.0f);
             out[(size_t)t * width + col] = from_f32<T>(total);
         }
     }
 }
 
 PLLM_EXPORT int pllm_moe_pair_glu(int dtype, const void* h, const int* ids, const void* w_gu, void* act, int n_tokens, int width,
-                                  int ff, int top, int experts, cudaStream_t stream) {
+                                  int ff, int top, int experts, int glu, float limit, cudaStream_t stream) {
     if (n_tokens <= 0) return PLLM_OK;
+    if (glu < GLU_SILU || glu > GLU_CLAMPED) return PLLM_ERR_SIZE;
     if (width <= 0 || ff <= 0 || top <= 0 || experts <= 0) return PLLM_ERR_SIZE;
     if ((size_t)width * sizeof(float) > 200 * 1024) return PLLM_ERR_LIMIT;
     PLLM_DISPATCH_DTYPE(dtype, {
         cudaFuncSetAttribute(moe_pair_glu_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((size_t)width * sizeof(float)));
         launch_chained(moe_pair_glu_kernel<T>, dim3(n_tokens * top, (ff + 8 * PAIR_CW - 1) / (8 * PAIR_CW)), dim3(256),
-                       (size_t)width * sizeof(float), stream, (const T*)h, ids, (const T*)w_gu, (T*)act, width, ff, top, experts);
+                       (size_t)width * sizeof(float), stream, (const T*)h, ids, (const T*)w_gu, (T*)act, width, ff, top, experts, glu, limit);
     });
     return launch_status();
 }
 
 PLLM_EXPORT int pllm_moe_pair_down(int dtype, const void* act, const void* h, const int* ids, const float* weights, const void* w_d,
                                    const void* shared, void* out, int n_tokens, int width, int ff, int top, int experts,
-                                   cudaStream_t stream) {
+                                   const float* shared_gate, cudaStream_t stream) {
     if (n_tokens <= 0) return PLLM_OK;
     if (width <= 0 || ff <= 0 || top <= 0 || experts <= 0) return PLLM_ERR_SIZE;
     if (top > MOE_MAX_TOP) return PLLM_ERR_LIMIT;
@@ -351,11 +364,11 @@ PLLM_EXPORT int pllm_moe_pair_down(int dtype, const void* act, const void* h, co
         if (n_tokens <= 4)
             launch_chained(moe_pair_down_kernel<T, 1>, dim3(n_tokens, (width + 7) / 8), dim3(256), (size_t)top * ff * sizeof(float),
                            stream, (const T*)act, (const T*)h, ids, weights, (const T*)w_d, (const T*)shared, (T*)out, width, ff, top,
-                           experts);
+                           experts, shared_gate);
         else
             launch_chained(moe_pair_down_kernel<T, 2>, dim3(n_tokens, (width + 15) / 16), dim3(256), (size_t)top * ff * sizeof(float),
                            stream, (const T*)act, (const T*)h, ids, weights, (const T*)w_d, (const T*)shared, (T*)out, width, ff, top,
-                           experts);
+                           experts, shared_gate);
     });
     return launch_status();
 }
@@ -426,12 +439,14 @@ __global__ void __launch_bounds__(256) moe_gather_kernel(const T* h, const int* 
 
 template <typename T>
 __global__ void __launch_bounds__(256) moe_combine_kernel(const T* y, const T* h, const int* pair_slot, const float* weights,
-                                                          const T* shared, T* __restrict__ out, int width, int top) {
+                                                          const T* shared, T* __restrict__ out, int width, int top,
+                                                          const float* shared_gate) {
     pdl_launch_dependents();
     pdl_wait(KID_MOE);
     const int t = blockIdx.x;
+    const float sg = shared_gate ? 1.0f / (1.0f + expf(-shared_gate[t])) : 1.0f;
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        float total = shared ? to_f32(shared[(size_t)t * width + c]) : 0.f;
+        float total = shared ? to_f32(shared[(size_t)t * width + c]) * sg : 0.f;
         for (int k = 0; k < top; k++) {
             const int slot = pair_slot[(size_t)t * top + k];
             const float v = slot < 0 ? to_f32(h[(size_t)t * width + c]) : to_f32(y[(size_t)slot * width + c]);
@@ -461,11 +476,12 @@ PLLM_EXPORT int pllm_moe_gather(int dtype, const void* h, const int* slot_pair, 
 }
 
 PLLM_EXPORT int pllm_moe_combine(int dtype, const void* y, const void* h, const int* pair_slot, const float* weights,
-                                 const void* shared, void* out, int n_tokens, int width, int top, cudaStream_t stream) {
+                                 const void* shared, void* out, int n_tokens, int width, int top, const float* shared_gate,
+                                 cudaStream_t stream) {
     if (n_tokens <= 0) return PLLM_OK;
     PLLM_DISPATCH_DTYPE(dtype, {
         launch_chained(moe_combine_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, (const T*)y, (const T*)h, pair_slot, weights,
-                       (const T*)shared, (T*)out, width, top);
+                       (const T*)shared, (T*)out, width, top, shared_gate);
     });
     return launch_status();
 }

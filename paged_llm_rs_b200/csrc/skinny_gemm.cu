@@ -49,7 +49,7 @@ __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1
 
 template <int MT, int NT, int EPI, typename OutT>
 __global__ void __launch_bounds__(16 * 32, 1) skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w,
-                                                                 OutT* __restrict__ y, int M, int N, int K) {
+                                                                 OutT* __restrict__ y, int M, int N, int K, int act, float limit) {
     static_assert(!EPI || NT % 2 == 0, "the gated epilogue pairs tiles of gate and up");
     // k blocks of 32 whose loads are issued together
     constexpr int U = MT == 1 ? 4 : (MT == 2 ? 2 : 1);
@@ -145,7 +145,7 @@ __global__ void __launch_bounds__(16 * 32, 1) skinny_gemm_kernel(const bf16* x, 
                 // gate and up are rounded as a product of their own would leave them
                 const float g = __bfloat162float(__float2bfloat16_rn(s));
                 u = __bfloat162float(__float2bfloat16_rn(u));
-                s = g / (1.0f + expf(-g)) * u;
+                s = glu_act(act, limit, g, u);
             }
             y[(size_t)m * N + n0 + c] = from_f32<OutT>(s);
         }
@@ -186,13 +186,14 @@ PLLM_EXPORT int pllm_skinny_gemm_glu_supports(int M, int N, int K) {
 }
 
 template <int MT, int NT, int EPI, typename OutT>
-static int launch_skinny(const void* x, const void* w, void* y, int M, int N, int K, int warps, cudaStream_t stream) {
+static int launch_skinny(const void* x, const void* w, void* y, int M, int N, int K, int warps, cudaStream_t stream,
+                         int act = GLU_SILU, float limit = 0.f) {
     const size_t smem = (warps > 1 || EPI) ? (size_t)warps * MT * 16 * NT * 8 * sizeof(float) : 0;
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(skinny_gemm_kernel<MT, NT, EPI, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     constexpr int out_cols = EPI ? 4 * NT : 8 * NT;
     launch_chained(skinny_gemm_kernel<MT, NT, EPI, OutT>, dim3(N / out_cols), dim3(warps * 32), smem, stream,
-                   (const bf16*)x, (const bf16*)w, (OutT*)y, M, N, K);
+                   (const bf16*)x, (const bf16*)w, (OutT*)y, M, N, K, act, limit);
     return launch_status();
 }
 
@@ -260,8 +261,9 @@ PLLM_EXPORT int pllm_skinny_gemm(const void* x, const void* w, void* y, int M, i
 }
 
 // w is [2N, K], gate rows then up rows, and y[M, N] = silu(x Wg^T) * (x Wu^T); up to 16 rows, all bfloat16.
-PLLM_EXPORT int pllm_skinny_gemm_glu(const void* x, const void* w, void* y, int M, int N, int K, cudaStream_t stream) {
-    if (!pllm_skinny_gemm_glu_supports(M, N, K)) return PLLM_ERR_SIZE;
+// (act, limit: the gated activation in place of silu, see common.cuh)
+PLLM_EXPORT int pllm_skinny_gemm_glu(const void* x, const void* w, void* y, int M, int N, int K, int act, float limit, cudaStream_t stream) {
+    if (!pllm_skinny_gemm_glu_supports(M, N, K) || act < GLU_SILU || act > GLU_CLAMPED) return PLLM_ERR_SIZE;
     if (((uintptr_t)x | (uintptr_t)w) & 15) return PLLM_ERR_ALIGN;
     // Tiles of 16 columns of y (16 gate rows and 16 up rows of W) where that gives four fifths of the SMs a CTA and
     // either the rows are long or the tiles are few enough to be in place at once; else of 8.  Measured at 8 rows,
@@ -272,10 +274,10 @@ PLLM_EXPORT int pllm_skinny_gemm_glu(const void* x, const void* w, void* y, int 
     if ((g_skinny_nt_override == 4 && N % 16 == 0) || g_skinny_nt_override == 2) nt = g_skinny_nt_override;
     if (nt == 4) {
         const int warps = pick_warps(K, N / 16, 128);
-        return launch_skinny<1, 4, 1, bf16>(x, w, y, M, N, K, warps, stream);
+        return launch_skinny<1, 4, 1, bf16>(x, w, y, M, N, K, warps, stream, act, limit);
     }
     const int warps = pick_warps(K, N / 8, 128);
-    return launch_skinny<1, 2, 1, bf16>(x, w, y, M, N, K, warps, stream);
+    return launch_skinny<1, 2, 1, bf16>(x, w, y, M, N, K, warps, stream, act, limit);
 }
 
 PLLM_TRACE_EXPORT(skinny_gemm)

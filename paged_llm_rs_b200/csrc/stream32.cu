@@ -7,6 +7,11 @@
 //   outnorm_add         x[r] += a[r] / sqrt(mean(a[r]^2) + eps) * gain;  h[r] = T(x[r])
 //                       (the norm sits on the sublayer's OUTPUT a, the sum stays in float)
 //   rmsnorm_from32      y[i] = T(x[r] / sqrt(mean(x[r]^2) + eps) * gain),  r = rows ? rows[i] : i
+//   embed_norm32        x[t] = e / sqrt(mean(e^2) + eps) * gain,  e = table[token[t]]       (a norm right behind the embedding)
+//   add_scaled_norm32   x[r] += mult * d[r]  (d may be absent);  y[i] = T(x[r] / sqrt(mean(x[r]^2) + eps) * gain)
+//                       (the pre-norm block of a float stream whose sublayer outputs are multiplied by a constant;
+//                       with rows the sum is formed for those rows only and not stored)
+//   scale32             x *= c
 //
 // All statistics, the gain multiply and the sum are float; each output is rounded once.
 #include "common.cuh"
@@ -231,6 +236,134 @@ PLLM_EXPORT int pllm_rmsnorm_from32(int dtype, const float* x, const float* gain
         launch_chained(rmsnorm_from32_kernel<T>, dim3((n_rows + rows_per_cta - 1) / rows_per_cta), dim3(256), 0, stream, x,
                        gain, (T*)y, rows, n_rows, width, eps, team);
     });
+    return launch_status();
+}
+
+// One CTA a token: the row is fetched once into registers-by-stride, its mean square reduced over the CTA.
+template <typename T>
+__global__ void __launch_bounds__(256) embed_norm32_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
+                                                           const float* __restrict__ gain, float* __restrict__ out, int hidden,
+                                                           int vocab, float eps, int* status) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait(KID_STREAM32);
+    const int t = blockIdx.x;
+    const int tok = tokens[t];
+    const bool ok = tok >= 0 && tok < vocab;
+    if (!ok && threadIdx.x == 0) atomicOr(status, 1);
+    const T* src = table + (size_t)(ok ? tok : 0) * hidden;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) { const float v = to_f32(src[i]); ss += v * v; }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+    float* dst = out + (size_t)t * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = ok ? to_f32(src[i]) * inv * gain[i] : 0.f;
+}
+
+PLLM_EXPORT int pllm_embed_norm32(int dtype, const int* tokens, const void* table, const float* gain, float* out, int n_tokens,
+                                  int hidden, int vocab, float eps, int* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return PLLM_OK;
+    if (hidden <= 0 || vocab <= 0) return PLLM_ERR_SIZE;
+    PLLM_DISPATCH_DTYPE(dtype, {
+        const int threads = min(256, max(32, (hidden + 31) / 32 * 32));
+        launch_chained(embed_norm32_kernel<T>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const T*)table, gain, out,
+                       hidden, vocab, eps, status);
+    });
+    return launch_status();
+}
+
+// Rows and teams as in outnorm_add.  The sum x + mult * d is formed once, kept in registers where the row is short
+// enough (ADD_KEEP values a lane) and formed again otherwise; it is stored only when every row is taken (rows null).
+#define ADD_KEEP 16
+template <typename T>
+__global__ void __launch_bounds__(256) add_scaled_norm32_kernel(float* x, const T* d, float mult, const float* __restrict__ gain,
+                                                                T* __restrict__ y, const int* __restrict__ rows, int n_rows,
+                                                                int width, float eps, int team) {
+    __shared__ float part[8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int member = (warp % team) * 32 + lane, lanes = team * 32;
+    const int rows_per_cta = 8 / team;
+    const int i = blockIdx.x * rows_per_cta + warp / team;
+    pdl_launch_dependents();
+    pdl_wait(KID_STREAM32);
+    const bool live = i < n_rows;
+    const size_t r = live ? (rows ? (size_t)rows[i] : (size_t)i) : 0;
+    float* xr = x + r * width;
+    const T* dr = d ? d + r * width : nullptr;
+    const bool store = d != nullptr && rows == nullptr;
+    float keep[ADD_KEEP];
+    float ss = 0.f;
+    if (live) {
+        int k = 0;
+        for (int c = member; c < width; c += lanes, k++) {
+            float v = xr[c];
+            if (dr) v += mult * to_f32(dr[c]);
+            if (store) xr[c] = v;
+            if (k < ADD_KEEP) keep[k] = v;
+            ss += v * v;
+        }
+    }
+    ss = warp_sum(ss);
+    if (team > 1) {
+        if (lane == 0) part[warp] = ss;
+        __syncthreads();
+        ss = 0.f;
+        const int first = warp / team * team;
+        for (int w = 0; w < team; w++) ss += part[first + w];
+    }
+    if (!live) return;
+    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+    T* yr = y + (size_t)i * width;
+    int k = 0;
+    for (int c = member; c < width; c += lanes, k++) {
+        float v;
+        if (k < ADD_KEEP) v = keep[k];
+        else { v = xr[c]; if (dr && !store) v += mult * to_f32(dr[c]); }
+        yr[c] = from_f32<T>(v * inv * gain[c]);
+    }
+}
+
+PLLM_EXPORT int pllm_add_scaled_norm32(int dtype, float* x, const void* d, float mult, const float* gain, void* y, const int* rows,
+                                       int n_rows, int width, float eps, cudaStream_t stream) {
+    if (n_rows <= 0) return PLLM_OK;
+    if (width <= 0) return PLLM_ERR_SIZE;
+    PLLM_DISPATCH_DTYPE(dtype, {
+        const int team = stream32_team(n_rows, width, 4);
+        const int rows_per_cta = 8 / team;
+        launch_chained(add_scaled_norm32_kernel<T>, dim3((n_rows + rows_per_cta - 1) / rows_per_cta), dim3(256), 0, stream, x,
+                       (const T*)d, mult, gain, (T*)y, rows, n_rows, width, eps, team);
+    });
+    return launch_status();
+}
+
+// x[r] += mult * d[r] for every row, nothing else (the last sublayer's output when no row is wanted of the step).
+template <typename T>
+__global__ void add_scaled32_kernel(float* x, const T* d, float mult, long long total) {
+    pdl_launch_dependents();
+    pdl_wait(KID_STREAM32);
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x)
+        x[i] += mult * to_f32(d[i]);
+}
+
+PLLM_EXPORT int pllm_add_scaled32(int dtype, float* x, const void* d, float mult, long long total, cudaStream_t stream) {
+    if (total <= 0) return PLLM_OK;
+    PLLM_DISPATCH_DTYPE(dtype, {
+        const int blocks = (int)min((long long)sm_count() * 8, (total + 255) / 256);
+        launch_chained(add_scaled32_kernel<T>, dim3(blocks), dim3(256), 0, stream, x, (const T*)d, mult, total);
+    });
+    return launch_status();
+}
+
+__global__ void scale32_kernel(float* x, float c, long long total) {
+    pdl_launch_dependents();
+    pdl_wait(KID_STREAM32);
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) x[i] *= c;
+}
+
+PLLM_EXPORT int pllm_scale32(float* x, float c, long long total, cudaStream_t stream) {
+    if (total <= 0) return PLLM_OK;
+    const int blocks = (int)min((long long)sm_count() * 8, (total + 255) / 256);
+    launch_chained(scale32_kernel, dim3(blocks), dim3(256), 0, stream, x, c, total);
     return launch_status();
 }
 

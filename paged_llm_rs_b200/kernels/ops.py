@@ -38,7 +38,7 @@ def lib():
         sig = {
             "pllm_embed": [c_int, P, P, P, c_int, c_int, c_int, P, P],
             "pllm_rmsnorm": [c_int, P, P, P, P, P, P, c_int, c_int, c_float, P],
-            "pllm_swiglu": [c_int, P, P, c_int, c_int, P],
+            "pllm_swiglu": [c_int, P, P, c_int, c_int, c_int, c_float, P],
             "pllm_qk_norm_rope_kv": [c_int, P, P, P, P, c_float, P, P, c_int, c_int, P, P, P, P,
                                      c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
             "pllm_attention_generic": [c_int, P, P, P, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int,
@@ -50,7 +50,7 @@ def lib():
             "pllm_skinny_gemm_supports": [c_int, c_int, c_int],
             "pllm_skinny_gemm": [P, P, P, c_int, c_int, c_int, c_int, P],
             "pllm_skinny_gemm_glu_supports": [c_int, c_int, c_int],
-            "pllm_skinny_gemm_glu": [P, P, P, c_int, c_int, c_int, P],
+            "pllm_skinny_gemm_glu": [P, P, P, c_int, c_int, c_int, c_int, c_float, P],
             "pllm_sm_count": [],
             "pllm_attention_mma_supports": [c_int, c_int, c_int, c_int],
             "pllm_attention_mma_tile_tokens": [c_int, c_int],
@@ -66,7 +66,7 @@ def lib():
         sig["pllm_attention_prefill_tcgen05_supports"] = [c_int] * 6
         sig["pllm_attention_prefill_tcgen05"] = [P] * 10 + [c_int] * 7 + [c_float, c_int, P, P]
         sig["pllm_gemm_tcgen05_supports"] = [c_int, c_int, c_int, c_int]
-        sig["pllm_gemm_tcgen05"] = [P, P, P, c_int, c_int, c_int, c_int, P, P]
+        sig["pllm_gemm_tcgen05"] = [P, P, P, c_int, c_int, c_int, c_int, c_float, P, P]
         sig["pllm_embed_scaled32"] = [c_int, P, P, P, c_int, c_int, c_int, c_float, P, P]
         sig["pllm_sinusoid_add"] = [P, P, P, c_int, c_int, P]
         sig["pllm_round_rows"] = [c_int, P, P, c_ll, P]
@@ -80,13 +80,21 @@ def lib():
         sig["pllm_latent_attention_mma_tile_tokens"] = [c_int]
         sig["pllm_latent_attention_mma_ctas_per_item"] = [c_int]
         sig["pllm_latent_attention_mma"] = [P, P, P, P, P, c_int, P, P, P] + [c_int] * 5 + [c_float, P, P]
-        sig["pllm_moe_route"] = [c_int, P, P, P, P, P] + [c_int] * 6 + [P]
+        sig["pllm_moe_route"] = [c_int, P, P, P, P, P] + [c_int] * 6 + [P, c_int, P, P]
         sig["pllm_moe_align"] = [P, c_int, c_int, P, P, P, c_int, P]
         sig["pllm_moe_gather"] = [c_int, P, P, P, P, c_int, c_int, c_int, P]
-        sig["pllm_moe_combine"] = [c_int, P, P, P, P, P, P, c_int, c_int, c_int, P]
-        sig["pllm_gemm_tcgen05_grouped"] = [P, P, P, c_int, c_int, c_int, c_int, P, c_int, P, P]
-        sig["pllm_moe_pair_glu"] = [c_int, P, P, P, P] + [c_int] * 5 + [P]
-        sig["pllm_moe_pair_down"] = [c_int, P, P, P, P, P, P, P] + [c_int] * 5 + [P]
+        sig["pllm_moe_combine"] = [c_int, P, P, P, P, P, P, c_int, c_int, c_int, P, P]
+        sig["pllm_gemm_tcgen05_grouped"] = [P, P, P, c_int, c_int, c_int, c_int, c_float, P, c_int, P, P]
+        sig["pllm_moe_pair_glu"] = [c_int, P, P, P, P] + [c_int] * 6 + [c_float, P]
+        sig["pllm_moe_pair_down"] = [c_int, P, P, P, P, P, P, P] + [c_int] * 5 + [P, P]
+        sig["pllm_embed_norm32"] = [c_int, P, P, P, P, c_int, c_int, c_int, c_float, P, P]
+        sig["pllm_add_scaled_norm32"] = [c_int, P, P, c_float, P, P, P, c_int, c_int, c_float, P]
+        sig["pllm_add_scaled32"] = [c_int, P, P, c_float, c_ll, P]
+        sig["pllm_scale32"] = [P, c_float, c_ll, P]
+        sig["pllm_rope_mix_kv_write"] = [c_int, P, c_int, P, P, c_int, P, P, P, P, c_int, P] + [c_int] * 6 + [c_ll, P, P]
+        sig["pllm_attention_sink"] = [c_int, P, P, P, P, P, c_int, P, P, P, P] + [c_int] * 9 + [c_float, c_float, P, P]
+        sig["pllm_attention_sink_tile_tokens"] = [c_int, c_int]
+        sig["pllm_mamba2_mix"] = [c_int] + [P] * 8 + [c_int, c_int, P, c_ll, P, P, P] + [c_int] * 7 + [c_float, P]
         sig["pllm_pack_decode_step"] = [P, c_int, c_int, P, P, P, P, P] + [c_int] * 16 + [P, P]
         for name, args in sig.items():
             fn = getattr(L, name)
@@ -182,13 +190,25 @@ def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor,
     return out
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[n, I] = silu(gate_up[n, :I]) * gate_up[n, I:]."""
+# The gated activations y = act(g, u) (csrc/common.cuh): silu(g) u; max(g, 0) u; and, with g' = min(g, limit) and
+# u' = clamp(u, -limit, limit), g' sigmoid(1.702 g') (u' + 1).
+GLU_KINDS = {"silu": 0, "relu": 1, "clamped": 2}
+
+
+def _glu(act: str) -> int:
+    try:
+        return GLU_KINDS[act]
+    except KeyError:
+        raise KernelError(f"gated activation {act!r} is not known; known: {sorted(GLU_KINDS)}") from None
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, act: str = "silu", limit: float = 0.0) -> torch.Tensor:
+    """out[n, I] = act(gate_up[n, :I], gate_up[n, I:]), silu(g) * u unless ``act`` names another gated activation."""
     _dev(gate_up, out)
     n, two_i = gate_up.shape
     if two_i % 2 or out.shape != (n, two_i // 2) or out.dtype != gate_up.dtype:
         raise KernelError("swiglu: out must be [n, I] for an input [n, 2I] of the same dtype")
-    _check(lib().pllm_swiglu(_code(gate_up), _ptr(gate_up), _ptr(out), n, two_i // 2, _stream()), "swiglu")
+    _check(lib().pllm_swiglu(_code(gate_up), _ptr(gate_up), _ptr(out), n, two_i // 2, _glu(act), float(limit), _stream()), "swiglu")
     return out
 
 
@@ -523,7 +543,8 @@ def gemm_tcgen05_takes(x, weight: torch.Tensor, n_out: int, glu: bool) -> bool:
         lib().pllm_gemm_tcgen05_supports(x.shape[0], n_out, weight.shape[1], 1 if glu else 0))
 
 
-def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, glu: bool = False, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, glu: bool = False, status: Optional[torch.Tensor] = None,
+                 act: str = "silu", limit: float = 0.0) -> torch.Tensor:
     """x W^T on the tcgen05 tensor cores (bfloat16, float accumulation); with ``glu`` W is
     [gate rows; up rows] and the result is silu(x Wg^T) * (x Wu^T)."""
     M, K = x.shape
@@ -533,8 +554,8 @@ def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, glu: bool = False, statu
     _dev(x, weight)
     out = torch.empty((M, n_out), dtype=torch.bfloat16, device=x.device)
     st = status if status is not None else gemm_status(x.device)
-    _check(lib().pllm_gemm_tcgen05(_ptr(x), _ptr(weight), _ptr(out), M, n_out, K, 1 if glu else 0, _ptr(st), _stream()),
-           "gemm_tcgen05")
+    _check(lib().pllm_gemm_tcgen05(_ptr(x), _ptr(weight), _ptr(out), M, n_out, K, 1 + _glu(act) if glu else 0, float(limit),
+                                   _ptr(st), _stream()), "gemm_tcgen05")
     return out
 
 
@@ -589,8 +610,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = 
     return torch.matmul(x, weight.t(), out=out) if out is not None else torch.matmul(x, weight.t())
 
 
-def linear_glu(x: torch.Tensor, w_gate_up: torch.Tensor, status: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """silu(x Wg^T) * (x Wu^T) for W = [Wg; Wu] stacked [2I, K]: the gated
+def linear_glu(x: torch.Tensor, w_gate_up: torch.Tensor, status: Optional[torch.Tensor] = None, act: str = "silu",
+               limit: float = 0.0) -> torch.Tensor:
+    """act(x Wg^T, x Wu^T), silu(g) * u unless ``act`` says otherwise, for W = [Wg; Wu] stacked [2I, K]: the gated
     feed-forward's first half (crates/pagedllm/src/model/layers.rs:93-99).  Few
     rows in bfloat16: one kernel whose CTAs hold the same columns of both halves;
     many rows: the tcgen05 product with the activation in its epilogue; otherwise
@@ -604,14 +626,13 @@ def linear_glu(x: torch.Tensor, w_gate_up: torch.Tensor, status: Optional[torch.
     if FUSE_GLU and skinny_glu_takes(x, w_gate_up, inter):
         _dev(x, w_gate_up)
         out = torch.empty((x.shape[0], inter), dtype=torch.bfloat16, device=x.device)
-        _check(lib().pllm_skinny_gemm_glu(_ptr(x), _ptr(w_gate_up), _ptr(out), x.shape[0], inter, K, _stream()),
-               "skinny_gemm_glu")
+        _check(lib().pllm_skinny_gemm_glu(_ptr(x), _ptr(w_gate_up), _ptr(out), x.shape[0], inter, K, _glu(act), float(limit),
+                                          _stream()), "skinny_gemm_glu")
         return out
     if TCGEN05_GEMM >= 1 and x.shape[0] >= TCGEN05_MIN_M and gemm_tcgen05_takes(x, w_gate_up, inter, True):
-        return gemm_tcgen05(x, w_gate_up, glu=True, status=status)
+        return gemm_tcgen05(x, w_gate_up, glu=True, status=status, act=act, limit=limit)
     gu = linear(x, w_gate_up)
-    act = torch.empty((gu.shape[0], inter), dtype=gu.dtype, device=gu.device)
-    return swiglu(gu, act)
+    return swiglu(gu, torch.empty((gu.shape[0], inter), dtype=gu.dtype, device=gu.device), act, limit)
 
 
 # ---- a residual stream kept in float32 (csrc/stream32.cu) ---------------------------------------------
@@ -768,27 +789,35 @@ def latent_attention(q: torch.Tensor, rows: torch.Tensor, block_tables: torch.Te
 
 # ---- mixture of experts (csrc/moe.cu) -----------------------------------------------------------------------
 
-def moe_route(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], top: int, groups: int, keep: int):
-    """The router: (ids int32 [T, top], weights float32 [T, top]).  w_router float32 [outputs, width]."""
-    _dev(h, w_router, correction)
-    _f32(w_router, "w_router"); _f32(correction, "correction")
+def moe_route(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], top: int, groups: int, keep: int,
+              bias: Optional[torch.Tensor] = None, extra: int = 0):
+    """The router: (ids int32 [T, top], weights float32 [T, top]).  w_router float32 [outputs + extra, width].
+    ``bias`` (float32 [outputs]) is added to the logits.  With ``extra`` the matrix carries that many further rows
+    behind the router's, and their products with h come back as a third value, float32 [T, extra]."""
+    _dev(h, w_router, correction, bias)
+    _f32(w_router, "w_router"); _f32(correction, "correction"); _f32(bias, "bias")
     T, W = h.shape
-    E = w_router.shape[0]
-    if w_router.shape[1] != W or (correction is not None and correction.numel() != E):
-        raise KernelError("moe_route: the router's weight or correction does not fit")
+    E = w_router.shape[0] - int(extra)
+    if w_router.shape[1] != W or E < 1 or any(t is not None and t.numel() != E for t in (correction, bias)):
+        raise KernelError("moe_route: the router's weight, correction or bias does not fit")
     ids = torch.empty((T, top), dtype=torch.int32, device=h.device)
     weights = torch.empty((T, top), dtype=torch.float32, device=h.device)
+    more = torch.empty((T, extra), dtype=torch.float32, device=h.device) if extra else None
     _check(lib().pllm_moe_route(_code(h), _ptr(h), _ptr(w_router), _ptr(correction), _ptr(ids), _ptr(weights), T, W, E,
-                                int(top), int(groups), int(keep), _stream()), "moe_route")
-    return ids, weights
+                                int(top), int(groups), int(keep), _ptr(bias), int(extra), _ptr(more), _stream()), "moe_route")
+    return (ids, weights, more) if extra else (ids, weights)
 
 
 def moe_experts_few(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gu: torch.Tensor, w_d: torch.Tensor,
-                    shared: Optional[torch.Tensor]) -> torch.Tensor:
+                    shared: Optional[torch.Tensor], act: str = "silu", limit: float = 0.0,
+                    shared_gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """sum_k weights[t, k] * expert_{ids[t, k]}(h[t]) (+ shared[t]); an id at or above the experts with tensors is the
-    identity.  w_gu [experts, 2 ff, width] (gate rows, then up rows), w_d [experts, width, ff].  The weight-streaming form."""
-    _dev(h, ids, weights, w_gu, w_d, shared)
-    _i32(ids, "ids"); _f32(weights, "weights")
+    identity.  w_gu [experts, 2 ff, width] (gate rows, then up rows), w_d [experts, width, ff].  The weight-streaming form.
+    ``act``, ``limit``: the experts' gated activation.  ``shared_gate`` (float32 [T]): shared[t] is multiplied by its sigmoid."""
+    _dev(h, ids, weights, w_gu, w_d, shared, shared_gate)
+    _i32(ids, "ids"); _f32(weights, "weights"); _f32(shared_gate, "shared_gate")
+    if shared_gate is not None and shared_gate.numel() != h.shape[0]:
+        raise KernelError("moe_experts_few: the shared expert's gate must hold one number a token")
     T, W = h.shape
     E, two_ff, _ = w_gu.shape
     ff, top = two_ff // 2, ids.shape[1]
@@ -796,12 +825,13 @@ def moe_experts_few(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w
         raise KernelError("moe_experts_few: expert weights do not fit")
     if shared is not None and (shared.shape != h.shape or shared.dtype != h.dtype):
         raise KernelError("moe_experts_few: the shared expert's output must have h's shape and dtype")
-    act = torch.empty((T * top, ff), dtype=h.dtype, device=h.device)
+    acts = torch.empty((T * top, ff), dtype=h.dtype, device=h.device)
     out = torch.empty_like(h)
     L = lib()
-    _check(L.pllm_moe_pair_glu(_code(h), _ptr(h), _ptr(ids), _ptr(w_gu), _ptr(act), T, W, ff, top, E, _stream()), "moe_pair_glu")
-    _check(L.pllm_moe_pair_down(_code(h), _ptr(act), _ptr(h), _ptr(ids), _ptr(weights), _ptr(w_d), _ptr(shared), _ptr(out),
-                                T, W, ff, top, E, _stream()), "moe_pair_down")
+    _check(L.pllm_moe_pair_glu(_code(h), _ptr(h), _ptr(ids), _ptr(w_gu), _ptr(acts), T, W, ff, top, E, _glu(act), float(limit),
+                               _stream()), "moe_pair_glu")
+    _check(L.pllm_moe_pair_down(_code(h), _ptr(acts), _ptr(h), _ptr(ids), _ptr(weights), _ptr(w_d), _ptr(shared), _ptr(out),
+                                T, W, ff, top, E, _ptr(shared_gate), _stream()), "moe_pair_down")
     return out
 
 
@@ -820,11 +850,12 @@ def moe_grouped_takes(h: torch.Tensor, w_gu: torch.Tensor, w_d: torch.Tensor) ->
 
 
 def moe_experts_grouped(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gu: torch.Tensor, w_d: torch.Tensor,
-                        shared: Optional[torch.Tensor], status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                        shared: Optional[torch.Tensor], status: Optional[torch.Tensor] = None, act: str = "silu",
+                        limit: float = 0.0, shared_gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The same sum as ``moe_experts_few`` by sorting the (token, expert) pairs by expert, two grouped tensor-core
     products (the first with the gated activation in its epilogue) and a weighted combine."""
-    _dev(h, ids, weights, w_gu, w_d, shared)
-    _i32(ids, "ids"); _f32(weights, "weights")
+    _dev(h, ids, weights, w_gu, w_d, shared, shared_gate)
+    _i32(ids, "ids"); _f32(weights, "weights"); _f32(shared_gate, "shared_gate")
     T, W = h.shape
     E, two_ff, _ = w_gu.shape
     ff, top = two_ff // 2, ids.shape[1]
@@ -838,7 +869,7 @@ def moe_experts_grouped(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tenso
     pair_slot = torch.empty(n_pairs, dtype=torch.int32, device=dev)
     tile_expert = torch.empty(max_tiles, dtype=torch.int32, device=dev)
     xs = torch.empty((slots, W), dtype=h.dtype, device=dev)
-    act = torch.empty((slots, ff), dtype=h.dtype, device=dev)
+    acts = torch.empty((slots, ff), dtype=h.dtype, device=dev)
     y = torch.empty((slots, W), dtype=h.dtype, device=dev)
     out = torch.empty_like(h)
     st = status if status is not None else gemm_status(dev)
@@ -846,18 +877,182 @@ def moe_experts_grouped(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tenso
     _check(L.pllm_moe_align(_ptr(ids), n_pairs, E, _ptr(slot_pair), _ptr(pair_slot), _ptr(tile_expert), max_tiles, _stream()),
            "moe_align")
     _check(L.pllm_moe_gather(_code(h), _ptr(h), _ptr(slot_pair), _ptr(tile_expert), _ptr(xs), slots, W, top, _stream()), "moe_gather")
-    _check(L.pllm_gemm_tcgen05_grouped(_ptr(xs), _ptr(w_gu), _ptr(act), slots, ff, W, 1, _ptr(tile_expert), E, _ptr(st), _stream()),
-           "gemm_tcgen05_grouped (gate/up)")
-    _check(L.pllm_gemm_tcgen05_grouped(_ptr(act), _ptr(w_d), _ptr(y), slots, W, ff, 0, _ptr(tile_expert), E, _ptr(st), _stream()),
+    _check(L.pllm_gemm_tcgen05_grouped(_ptr(xs), _ptr(w_gu), _ptr(acts), slots, ff, W, 1 + _glu(act), float(limit), _ptr(tile_expert),
+                                       E, _ptr(st), _stream()), "gemm_tcgen05_grouped (gate/up)")
+    _check(L.pllm_gemm_tcgen05_grouped(_ptr(acts), _ptr(w_d), _ptr(y), slots, W, ff, 0, 0.0, _ptr(tile_expert), E, _ptr(st), _stream()),
            "gemm_tcgen05_grouped (down)")
     _check(L.pllm_moe_combine(_code(h), _ptr(y), _ptr(h), _ptr(pair_slot), _ptr(weights), _ptr(shared), _ptr(out), T, W, top,
-                              _stream()), "moe_combine")
+                              _ptr(shared_gate), _stream()), "moe_combine")
     return out
 
 
 def moe_experts(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gu: torch.Tensor, w_d: torch.Tensor,
-                shared: Optional[torch.Tensor], status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                shared: Optional[torch.Tensor], status: Optional[torch.Tensor] = None, act: str = "silu", limit: float = 0.0,
+                shared_gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The routed experts' weighted sum (+ the shared expert's output), by the form that fits the step."""
     if moe_grouped_takes(h, w_gu, w_d):
-        return moe_experts_grouped(h, ids, weights, w_gu, w_d, shared, status)
-    return moe_experts_few(h, ids, weights, w_gu, w_d, shared)
+        return moe_experts_grouped(h, ids, weights, w_gu, w_d, shared, status, act, limit, shared_gate)
+    return moe_experts_few(h, ids, weights, w_gu, w_d, shared, act, limit, shared_gate)
+
+
+# ---- a float32 stream with pre-norm blocks (csrc/stream32.cu) ----------------------------------------------------
+
+def embed_norm32(tokens: torch.Tensor, table: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor,
+                 status: torch.Tensor) -> torch.Tensor:
+    """out[t] = rmsnorm(table[tokens[t]]) * gain as float32, whatever the table's dtype."""
+    _dev(tokens, table, gain, out, status)
+    _i32(tokens, "tokens"); _f32(out, "out"); _f32(gain, "gain")
+    T, (V, H) = tokens.numel(), table.shape
+    if out.shape != (T, H) or gain.numel() != H:
+        raise KernelError(f"embed_norm32: out is {tuple(out.shape)}, expected {(T, H)}, with a gain of {H}")
+    _check(lib().pllm_embed_norm32(_code(table), _ptr(tokens), _ptr(table), _ptr(gain), _ptr(out), T, H, V, float(eps),
+                                   _ptr(status), _stream()), "embed_norm32")
+    return out
+
+
+def add_scaled_norm32(x: torch.Tensor, delta: Optional[torch.Tensor], mult: float, gain: torch.Tensor, eps: float,
+                      out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x (float32, in place) += mult * delta where delta is given; out[i] = rmsnorm(x[r]) * gain, r = rows[i] or i.
+    With ``rows`` the sum is formed for those rows only and x is left as it is."""
+    _dev(x, delta, gain, out, rows)
+    _f32(x, "x"); _f32(gain, "gain"); _i32(rows, "rows")
+    W = x.shape[-1]
+    n = rows.numel() if rows is not None else x.shape[0]
+    if gain.numel() != W or out.shape != (n, W) or (delta is not None and (delta.shape != x.shape or delta.dtype != out.dtype)):
+        raise KernelError("add_scaled_norm32: out, gain or delta does not fit")
+    _check(lib().pllm_add_scaled_norm32(_code(out), _ptr(x), _ptr(delta), float(mult), _ptr(gain), _ptr(out), _ptr(rows), n, W,
+                                        float(eps), _stream()), "add_scaled_norm32")
+    return out
+
+
+def add_scaled32(x: torch.Tensor, delta: torch.Tensor, mult: float) -> torch.Tensor:
+    """x (float32, in place) += mult * delta."""
+    _dev(x, delta)
+    _f32(x, "x")
+    if delta.shape != x.shape:
+        raise KernelError("add_scaled32: delta must have x's shape")
+    _check(lib().pllm_add_scaled32(_code(delta), _ptr(x), _ptr(delta), float(mult), x.numel(), _stream()), "add_scaled32")
+    return x
+
+
+def scale32(x: torch.Tensor, c: float) -> torch.Tensor:
+    """x (float32, in place) *= c."""
+    _dev(x)
+    _f32(x, "x")
+    _check(lib().pllm_scale32(_ptr(x), float(c), x.numel(), _stream()), "scale32")
+    return x
+
+
+# ---- attention with a capped score, a window that keeps the first tokens, and a sink (csrc/attention_sink.cu) ------
+
+def rope_mix_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, inv_freq: Optional[torch.Tensor], rot: int, positions: torch.Tensor,
+                      slots: Optional[torch.Tensor], kv_pool: Optional[torch.Tensor], v_first: Optional[torch.Tensor],
+                      lam: Optional[torch.Tensor], num_heads: int, num_kv_heads: int, dk: int, dv: int,
+                      status: torch.Tensor) -> torch.Tensor:
+    """qkv [T, heads dk + kv_heads (dk + dv)]: q and k rotated on their first ``rot`` entries (entry i with i + rot/2, the
+    angle position * inv_freq[i] a float32 product), q to q_out [T, heads dk], k | v to row ``slots[t]`` of kv_pool
+    [pages, kv_heads, page_size, dk + dv] (a negative slot, or no pool, writes nothing).  ``v_first``: a view
+    [T, kv_heads dv] (rows may be strided) of an earlier layer's values; v <- (1 - lam) v + lam v_first, lam one float32
+    on the device."""
+    _dev(qkv, q_out, inv_freq, positions, slots, kv_pool, lam, status)
+    _f32(inv_freq, "inv_freq"); _f32(lam, "lam"); _i32(positions, "positions"); _i32(slots, "slots")
+    T = qkv.shape[0]
+    if qkv.shape != (T, num_heads * dk + num_kv_heads * (dk + dv)) or q_out.numel() != T * num_heads * dk or q_out.dtype != qkv.dtype:
+        raise KernelError("rope_mix_kv_write: qkv or q_out does not fit the head counts and sizes")
+    if rot and (inv_freq is None or inv_freq.numel() * 2 != rot):
+        raise KernelError("rope_mix_kv_write: inv_freq must hold rot / 2 frequencies")
+    if positions.numel() < T or (slots is not None and slots.numel() < T):
+        raise KernelError("rope_mix_kv_write: positions / slots shorter than the tokens")
+    page_size, pool_rows = 1, 0
+    if kv_pool is not None:
+        if kv_pool.dim() != 4 or kv_pool.shape[1] != num_kv_heads or kv_pool.shape[3] != dk + dv or kv_pool.dtype != qkv.dtype:
+            raise KernelError(f"rope_mix_kv_write: the pool must be [pages, {num_kv_heads}, page_size, {dk + dv}] of {qkv.dtype}")
+        page_size, pool_rows = kv_pool.shape[2], kv_pool.shape[0] * kv_pool.shape[2]
+    vf_stride = 0
+    if v_first is not None:
+        if not v_first.is_cuda or v_first.dtype != qkv.dtype or v_first.shape != (T, num_kv_heads * dv) or v_first.stride(1) != 1 \
+                or lam is None:
+            raise KernelError("rope_mix_kv_write: v_first must be [T, kv_heads dv] of qkv's dtype with unit inner stride, and lam given")
+        vf_stride = v_first.stride(0)
+    _check(lib().pllm_rope_mix_kv_write(_code(qkv), _ptr(qkv), qkv.shape[1], _ptr(q_out), _ptr(inv_freq), int(rot), _ptr(positions),
+                                        _ptr(slots), _ptr(kv_pool), _ptr(v_first), vf_stride, _ptr(lam), T, num_heads, num_kv_heads,
+                                        dk, dv, page_size, pool_rows, _ptr(status), _stream()), "rope_mix_kv_write")
+    return q_out
+
+
+def attention_sink_tile_tokens(num_heads: int, num_kv_heads: int) -> int:
+    return int(lib().pllm_attention_sink_tile_tokens(int(num_heads), int(num_kv_heads)))
+
+
+def attention_sink(q: torch.Tensor, kv_pool: torch.Tensor, block_tables: torch.Tensor, w, out: torch.Tensor,
+                   sinks: Optional[torch.Tensor], num_heads: int, num_kv_heads: int, dk: int, dv: int, window: int, keep_first: int,
+                   scale: float, cap: float, status: torch.Tensor) -> torch.Tensor:
+    """Attention of the step's tokens over rows [k | v] of the paged pool [pages, kv_heads, page_size, dk + dv]:
+    score = cap tanh(scale q.k / cap) (cap 0: uncapped); key j is seen from position p when j <= p and (p - j < window or
+    j < keep_first) (window 0: every j <= p); the softmax's denominator also holds exp(sinks[head]).  ``w`` is the group's
+    ``AttentionWork``; then the reduction of split items.  q [T, heads, dk], out [T, heads, dv]."""
+    work, n_work, max_work, red, n_red, max_red = w.work, w.n_work, w.max_work, w.red, w.n_red, w.max_red
+    part_o, part_ml = w.part_o, w.part_ml
+    _dev(q, kv_pool, block_tables, work, n_work, out, part_o, part_ml, red, n_red, sinks, status)
+    for t, n in ((block_tables, "block_tables"), (work, "work"), (n_work, "n_work"), (red, "red"), (n_red, "n_red")):
+        _i32(t, n)
+    _f32(part_o, "part_o"); _f32(part_ml, "part_ml"); _f32(sinks, "sinks")
+    T = q.shape[0]
+    if kv_pool.dim() != 4 or kv_pool.shape[1] != num_kv_heads or kv_pool.shape[3] != dk + dv or kv_pool.dtype != q.dtype:
+        raise KernelError(f"attention_sink: the pool must be [pages, {num_kv_heads}, page_size, {dk + dv}] of q's dtype")
+    if q.numel() != T * num_heads * dk or out.numel() != T * num_heads * dv or out.dtype != q.dtype:
+        raise KernelError("attention_sink: q must be [T, heads, dk] and out [T, heads, dv]")
+    if part_o.shape[1:] != (num_heads, dv) or part_ml.shape[1:] != (num_heads, 2):
+        raise KernelError("attention_sink: the scratch for partial results is not [rows, heads, dv] and [rows, heads, 2]")
+    if sinks is not None and sinks.numel() != num_heads:
+        raise KernelError("attention_sink: one sink a head")
+    if work.numel() < max_work * 8 or red.numel() < max_red * 4:
+        raise KernelError("attention_sink: work / red lists shorter than their maxima")
+    n_pages, page_size = kv_pool.shape[0], kv_pool.shape[2]
+    L = lib()
+    _check(L.pllm_attention_sink(_code(q), _ptr(q), _ptr(kv_pool), _ptr(block_tables), _ptr(work), _ptr(n_work), max_work, _ptr(out),
+                                 _ptr(part_o), _ptr(part_ml), _ptr(sinks), num_heads, num_kv_heads, dk, dv, page_size, n_pages,
+                                 block_tables.shape[-1], int(window), int(keep_first), float(scale), float(cap), _ptr(status),
+                                 _stream()), "attention_sink")
+    _check(L.pllm_attention_reduce(_code(q), _ptr(part_o), _ptr(part_ml), _ptr(red), _ptr(n_red), max_red, _ptr(out), num_heads, dv,
+                                   1 if (w.many_splits and dv * 4 <= 1024) else 0, _stream()), "attention_reduce")
+    return out
+
+
+# ---- the Mamba-2 mixer between its projections (csrc/mamba2.cu) ------------------------------------------------------
+
+def mamba2_state_floats(heads: int, groups: int, vdim: int, state: int, taps: int) -> int:
+    """Floats of a request's state slot: every head's state matrix, then each channel's last taps - 1 inputs."""
+    return heads * state * vdim + (taps - 1) * (heads * vdim + 2 * groups * state)
+
+
+def mamba2_mix(u: torch.Tensor, conv_w: torch.Tensor, conv_b: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor,
+               d_skip: torch.Tensor, gain: torch.Tensor, segments: torch.Tensor, max_segment_tokens: int, state: torch.Tensor,
+               out: torch.Tensor, heads: int, groups: int, vdim: int, n_state: int, taps: int, norm_groups: int,
+               eps: float) -> torch.Tensor:
+    """From the input projection's u [T, 2 inner + 2 groups n_state + heads] to the output projection's input
+    [T, inner]: convolution and silu, the recurrence over each segment's tokens from and into its state slot, the gate
+    and the grouped norm.  ``segments`` int32 [n, 4] on the device: first token, tokens, tokens before, state slot."""
+    _dev(u, conv_w, conv_b, dt_bias, a_log, d_skip, gain, segments, state, out)
+    for t, n in ((dt_bias, "dt_bias"), (a_log, "a_log"), (d_skip, "d_skip"), (gain, "gain"), (state, "state")):
+        _f32(t, n)
+    _i32(segments, "segments")
+    T = u.shape[0]
+    inner, channels = heads * vdim, heads * vdim + 2 * groups * n_state
+    if u.shape != (T, inner + channels + heads) or out.shape != (T, inner) or out.dtype != u.dtype:
+        raise KernelError("mamba2_mix: u must be [T, 2 inner + 2 groups state + heads] and out [T, inner] of one dtype")
+    if conv_w.shape != (channels, taps) or conv_b.numel() != channels or conv_w.dtype != u.dtype or conv_b.dtype != u.dtype:
+        raise KernelError("mamba2_mix: the convolution's taps must be [channels, taps] and its bias [channels], of u's dtype")
+    if min(dt_bias.numel(), a_log.numel(), d_skip.numel()) != heads or gain.numel() != inner:
+        raise KernelError("mamba2_mix: one dt_bias, A_log and D a head, and a gain of inner entries")
+    if state.dim() != 2 or state.shape[1] < mamba2_state_floats(heads, groups, vdim, n_state, taps):
+        raise KernelError("mamba2_mix: the state slots are too small")
+    if segments.dim() != 2 or segments.shape[1] != 4:
+        raise KernelError("mamba2_mix: segments must be [n, 4]")
+    c_buf = torch.empty((T, channels), dtype=torch.float32, device=u.device)
+    y_buf = torch.zeros((T, inner), dtype=torch.float32, device=u.device)      # (rows of no segment, a captured step's padding, stay zero)
+    _check(lib().pllm_mamba2_mix(_code(u), _ptr(u), _ptr(conv_w), _ptr(conv_b), _ptr(dt_bias), _ptr(a_log), _ptr(d_skip), _ptr(gain),
+                                 _ptr(segments), segments.shape[0], int(max_segment_tokens), _ptr(state), state.stride(0),
+                                 _ptr(c_buf), _ptr(y_buf), _ptr(out), T, heads, groups, vdim, n_state, taps, norm_groups,
+                                 float(eps), _stream()), "mamba2_mix", launches=3)
+    return out

@@ -1,2 +1,3 @@
 from . import qwen3  # registers Qwen3ForCausalLM
 from . import surelorn  # registers Surelorn
+from . import bumisun  # registers Bumisun

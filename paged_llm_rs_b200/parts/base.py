@@ -56,7 +56,11 @@ class PagedNeed:
     takes back.  kind "full": everything stays until the request ends; "window": only the last
     ``window`` tokens are ever read, so older pages are given back.  A need says how its pages lie
     in memory; needs with equal ``group_key()`` share pages, an allocator and block tables.
-    Every need has the fields ``kind``, ``window`` and ``dtype`` (None: the model's dtype)."""
+    Every need has the fields ``kind``, ``window`` and ``dtype`` (None: the model's dtype).  A window need may also
+    say ``keep_first``: the pages that hold a request's first ``keep_first`` tokens stay with it whatever the window
+    has passed."""
+
+    keep_first = 0
 
     def group_key(self) -> tuple:
         raise NotImplementedError
@@ -98,6 +102,35 @@ class KVNeed(PagedNeed):
 
     def bytes_per_token(self, element_size):
         return 2 * self.num_kv_heads * self.head_dim * element_size
+
+
+@dataclass(frozen=True)
+class JoinedKVNeed(PagedNeed):
+    """Paged keys and values whose sizes may differ, a token's key and value side by side in one row a kv head:
+    a layer's rows as [pages, kv_heads, page_size, key_dim + value_dim].  With kind "window" only the last ``window``
+    tokens and the first ``keep_first`` are ever read."""
+
+    kind: str
+    num_kv_heads: int
+    key_dim: int
+    value_dim: int
+    window: Optional[int] = None
+    keep_first: int = 0
+    group_size: int = 1          # query heads to a kv head (mixers that cut their attention alike share work items)
+    dtype: Optional[torch.dtype] = None
+
+    def group_key(self) -> tuple:
+        return ("joined_kv", self.kind, self.window, self.keep_first, self.num_kv_heads, self.key_dim, self.value_dim,
+                self.group_size, self.dtype)
+
+    def pool_shape(self, entries, pages, page_size):
+        return (entries, pages, self.num_kv_heads, page_size, self.key_dim + self.value_dim)
+
+    def layer_view(self, pool, index):
+        return (pool[index],)
+
+    def bytes_per_token(self, element_size):
+        return self.num_kv_heads * (self.key_dim + self.value_dim) * element_size
 
 
 @dataclass(frozen=True)
@@ -193,6 +226,9 @@ class StepState:
     # per wanted row, for the sampling kernel: temperature (<= 0: greedy) and the request's uniform number
     temperature: torch.Tensor = None
     uniform: torch.Tensor = None
+    # what a layer hands to later layers of the same step (an early layer's values that later ones mix in, say), by name;
+    # emptied when a step's forward pass begins
+    carry: Dict[str, torch.Tensor] = field(default_factory=dict)
 
 
 # --- parts ------------------------------------------------------------------------

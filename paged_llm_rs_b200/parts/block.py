@@ -53,5 +53,30 @@ class OutputNormResidualBlock(Block):
         return stream, None
 
 
+class PreNormStreamBlock(Block):
+    """x + m mixer(norm(x)), then x + m ff(norm(x)), on a float32 stream: the pre-norm block with its norms
+    ``ScaledStreamRMSNorm``s, which add the pending sublayer output (times the model's constant m) into the stream
+    and norm the sum into the compute dtype in one kernel.  A layer may have no feed-forward: the mixer's output is
+    then what is handed on."""
+
+    def pre_mixer(self, stream, delta):
+        return self.norms["mixer"].add_norm(stream, delta)
+
+    def post_mixer(self, stream, a, step):
+        out = a
+        if self.feed_forward is not None:
+            out = self.feed_forward.forward(self.norms["feed_forward"].add_norm(stream, a), step)
+        rt = self.mixer.rt
+        if rt.trace is not None and self.prefix:
+            rt.record(f"{self.prefix}.out", stream + self.norms["mixer"].mult * out.float())
+        return stream, out
+
+    def forward(self, stream, delta, step, cache, writes_cache=True):
+        h = self.pre_mixer(stream, delta)
+        a = self.mixer.forward(h, step, cache, writes_cache)
+        return self.post_mixer(stream, a, step)
+
+
 register_block("prenorm_residual", PreNormResidualBlock)
+register_block("prenorm_stream32", PreNormStreamBlock)
 register_block("outnorm_residual", OutputNormResidualBlock)

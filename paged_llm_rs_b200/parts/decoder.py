@@ -12,8 +12,8 @@ from typing import Dict, List, Optional
 
 import torch
 
-from . import (attention, block, embedding, feed_forward, latent_attention, norm, position,  # noqa: F401  (register the parts)
-               routed_feed_forward)
+from . import (attention, block, embedding, feed_forward, latent_attention, mamba2, norm, position,  # noqa: F401  (register the parts)
+               routed_feed_forward, sink_attention)
 from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, Runtime, StepState,
                    make)
 from .spec import ModelSpec, TensorSpec
@@ -74,6 +74,7 @@ class DecoderModel:
         (for a step that is being captured): called as outside(fn, like) for every mixer that is
         not ``graph_safe``; it runs fn() outside the capture, now and at every replay, and returns
         a tensor shaped like ``like`` that holds fn()'s result each time."""
+        step.carry = {}
         residual = self.embedding.forward(step.tokens)
         for encoding in self.position_encodings.values():
             residual = encoding.at_embedding(residual, step)

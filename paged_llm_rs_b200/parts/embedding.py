@@ -47,6 +47,33 @@ class TokenEmbedding(Part):
         return out
 
 
+class NormedTokenEmbedding(Part):
+    """A row gather with an RMS norm right behind it, into a float32 residual stream: x = norm(table[token]) * gain.
+    ``norm`` names the gain's tensor."""
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        p = spec.params
+        self.vocab, self.hidden, self.eps = int(p["vocab_size"]), int(p["hidden_size"]), float(p["eps"])
+        self.leaf, self.norm_name = p.get("leaf", "weight"), p["norm"]
+        self.table = self.gain = None
+
+    def _table_name(self):
+        return self._name(self.leaf) if self.leaf else self.prefix
+
+    def tensors(self):
+        return [TensorSpec(self._table_name(), (self.vocab, self.hidden)), TensorSpec(self.norm_name, (self.hidden,), "gain")]
+
+    def bind(self, tensors):
+        self.table, self.gain = tensors[self._table_name()], tensors[self.norm_name]
+
+    def forward(self, tokens: torch.Tensor) -> torch.Tensor:
+        out = torch.empty((tokens.numel(), self.hidden), dtype=torch.float32, device=self.table.device)
+        ops.embed_norm32(tokens, self.table, self.gain, self.eps, out, self.rt.status)
+        self.rt.record(self._name("out"), out)
+        return out
+
+
 class LinearHead(Part):
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
@@ -54,6 +81,7 @@ class LinearHead(Part):
         self.vocab, self.hidden = int(p["vocab_size"]), int(p["hidden_size"])
         self.tied, self.tied_to = bool(p.get("tied", False)), p.get("tied_to")
         self.leaf = p.get("leaf", "weight")
+        self.scale = float(p.get("scale", 1.0))             # logits = (W x) * scale
         self.weight = None
 
     def _name(self, leaf: str) -> str:
@@ -78,9 +106,12 @@ class LinearHead(Part):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         logits = ops.linear(x, self.weight, out_dtype=torch.float32)
+        if self.scale != 1.0:
+            ops.scale32(logits, self.scale)
         self.rt.record(self._name("out"), logits)
         return logits
 
 
 register_embedding("token_embedding", TokenEmbedding)
+register_embedding("normed_token_embedding", NormedTokenEmbedding)
 register_head("linear_head", LinearHead)

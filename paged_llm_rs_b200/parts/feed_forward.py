@@ -1,7 +1,9 @@
-"""The gated feed-forward, down(silu(gate(x)) * up(x))
-(crates/pagedllm/src/model/layers.rs:67-106).  gate and up are one matrix
-product over the stacked weights, with the activation in its epilogue for the
-few rows of a decode step and as a kernel of its own otherwise."""
+"""The gated feed-forward, down(act(gate(x), up(x))), act(g, u) = silu(g) * u
+(crates/pagedllm/src/model/layers.rs:67-106) unless ``activation`` names another
+gated activation of the kernels ("relu": max(g, 0) * u; "clamped", with ``limit``).
+gate and up are one matrix product over the stacked weights, with the activation
+in its epilogue for the few rows of a decode step and for the many of a prompt
+portion, and as a kernel of its own otherwise."""
 
 from __future__ import annotations
 
@@ -20,6 +22,9 @@ class SwiGLUMLP(FeedForward):
         # the three tensors' leaves under the prefix (another checkpoint layout names them otherwise)
         self.names = dict(gate="gate_proj.weight", up="up_proj.weight", down="down_proj.weight")
         self.names.update(spec.params.get("names", {}))
+        self.activation, self.limit = spec.params.get("activation", "silu"), float(spec.params.get("limit", 0.0))
+        if self.activation not in ops.GLU_KINDS:
+            raise ValueError(f"activation {self.activation!r} is not known; known: {sorted(ops.GLU_KINDS)}")
         self.w_gate_up = self.w_down = None
 
     def tensors(self):
@@ -34,7 +39,7 @@ class SwiGLUMLP(FeedForward):
         self.w_down = tensors[self._name(n["down"])]
 
     def forward(self, x, step):
-        act = ops.linear_glu(x, self.w_gate_up, status=self.rt.status)
+        act = ops.linear_glu(x, self.w_gate_up, status=self.rt.status, act=self.activation, limit=self.limit)
         out = ops.linear(act, self.w_down, status=self.rt.status)
         if self.rt.trace is not None:
             self.rt.record(self._name("down_proj.in"), act)

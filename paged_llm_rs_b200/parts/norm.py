@@ -73,5 +73,28 @@ class StreamRMSNorm(RMSNorm):
         return stream if h is None else h
 
 
+class ScaledStreamRMSNorm(RMSNorm):
+    """RMSNorm in a pre-norm decoder whose residual stream stays float32 and whose sublayer outputs are multiplied by
+    one constant ``mult`` as they are added: ``add_norm`` does stream += mult * delta (in place) and norms the sum into
+    the compute dtype, in one kernel."""
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        self.mult = float(spec.params.get("mult", 1.0))
+
+    def forward(self, x, rows=None):
+        return self.add_norm(x, None, rows)
+
+    def add_norm(self, residual, delta, rows=None):
+        if residual.dtype != torch.float32:
+            raise ValueError("the residual stream of this norm is float32")
+        n = rows.numel() if rows is not None else residual.shape[0]
+        out = torch.empty((n, self.width), dtype=self.rt.dtype, device=residual.device)
+        ops.add_scaled_norm32(residual, delta, self.mult, self.gain, self.eps, out, rows=rows)
+        self.rt.record(self._name("out"), out)
+        return out
+
+
 register_norm("rmsnorm", RMSNorm)
 register_norm("rmsnorm_stream32", StreamRMSNorm)
+register_norm("rmsnorm_scaled_stream32", ScaledStreamRMSNorm)

@@ -9,9 +9,16 @@ Per token, with h the input (all router arithmetic in float32):
     the ``top`` largest choices are taken; weight_k = s_k / (sum of the chosen s + 1e-20)
     out = sum_k weight_k * E_k(h)  (+ S(h))
 
-E_k is expert k's down(silu(gate h) * up h); the LAST ``identity`` router outputs have no
-tensors and return h itself; S is an optional expert of the same form that every token uses.
-Counts, sizes and tensor leaves are parameters.  The router and the experts are kernels of
+E_k is expert k's down(act(gate h, up h)), act(g, u) = silu(g) * u unless ``activation`` (with
+``limit``) names another gated activation; the LAST ``identity`` router outputs have no
+tensors and return h itself; S is an optional expert of the same form (``shared_activation``,
+``shared_limit``) that every token uses.
+
+Options for routers of another make: ``router_bias`` adds a learned vector to W_r h before the
+softmax; without a correction the choice is then by the largest logits and the weights are the
+softmax over the chosen logits alone (s_k over the sum of the chosen s is exactly that).
+``shared_gate`` multiplies S(h) by sigmoid(w_sg . h), one number a token; w_sg rides as one more
+row of the router's float32 matrix.  Counts, sizes and tensor leaves are parameters.  The router and the experts are kernels of
 this library (csrc/moe.cu); the shared expert runs as the dense gated feed-forward does.
 """
 
@@ -33,13 +40,19 @@ class RoutedExperts(FeedForward):
         self.groups, self.keep = int(p.get("groups", 1)), int(p.get("keep", 1))
         self.shared_ff = p.get("shared_size")
         self.corrected = bool(p.get("correction", True))
+        self.router_bias, self.shared_gate = bool(p.get("router_bias", False)), bool(p.get("shared_gate", False))
+        self.activation, self.limit = p.get("activation", "silu"), float(p.get("limit", 0.0))
+        self.shared_activation, self.shared_limit = p.get("shared_activation", self.activation), float(p.get("shared_limit", self.limit))
+        if self.shared_gate and not self.shared_ff:
+            raise ValueError("shared_gate without a shared expert")
         outputs = self.experts + self.identity
         if outputs % self.groups or self.keep > self.groups or self.top > self.keep * (outputs // self.groups):
             raise ValueError(f"{outputs} router outputs, {self.groups} groups of which {self.keep} are kept, top {self.top}: "
                              "these do not fit together")
-        self.names = dict(router="router", correction="correction", expert="e{}", gate="gate", up="up", down="down", shared="shared")
+        self.names = dict(router="router", correction="correction", expert="e{}", gate="gate", up="up", down="down", shared="shared",
+                          router_bias="router.b", shared_gate="sg")
         self.names.update(p.get("names", {}))
-        self.w_router = self.correction = self.w_gu = self.w_d = self.ws_gu = self.ws_d = None
+        self.w_router = self.correction = self.w_gu = self.w_d = self.ws_gu = self.ws_d = self.bias = None
 
     def _expert(self, e: int, leaf: str) -> str:
         return self._name(f"{self.names['expert'].format(e)}.{self.names[leaf]}")
@@ -52,6 +65,10 @@ class RoutedExperts(FeedForward):
         t = [TensorSpec(self._name(self.names["router"]), (outputs, W), "matrix32")]
         if self.corrected:
             t.append(TensorSpec(self._name(self.names["correction"]), (outputs,), "offset"))
+        if self.router_bias:
+            t.append(TensorSpec(self._name(self.names["router_bias"]), (outputs,), "offset"))
+        if self.shared_gate:
+            t.append(TensorSpec(self._shared("shared_gate"), (1, W), "matrix32"))
         for e in range(self.experts):
             t += [TensorSpec(self._expert(e, "gate"), (ff, W)), TensorSpec(self._expert(e, "up"), (ff, W)),
                   TensorSpec(self._expert(e, "down"), (W, ff))]
@@ -64,6 +81,9 @@ class RoutedExperts(FeedForward):
     def bind(self, tensors):
         self.w_router = tensors[self._name(self.names["router"])]
         self.correction = tensors[self._name(self.names["correction"])] if self.corrected else None
+        self.bias = tensors[self._name(self.names["router_bias"])] if self.router_bias else None
+        if self.shared_gate:      # one more row of the router's matrix: its product leaves the router kernel as it is
+            self.w_router = torch.cat([self.w_router, tensors[self._shared("shared_gate")]], 0).contiguous()
         # experts stacked: [E, 2 ff, W] (an expert's gate rows, then its up rows) and [E, W, ff]
         self.w_gu = torch.stack([torch.cat([tensors[self._expert(e, "gate")], tensors[self._expert(e, "up")]], 0)
                                  for e in range(self.experts)], 0).contiguous()
@@ -74,9 +94,16 @@ class RoutedExperts(FeedForward):
 
     def forward(self, x, step):
         st = self.rt.status
-        ids, weights = ops.moe_route(x, self.w_router, self.correction, self.top, self.groups, self.keep)
-        shared = ops.linear(ops.linear_glu(x, self.ws_gu, status=st), self.ws_d, status=st) if self.shared_ff else None
-        out = ops.moe_experts(x, ids, weights, self.w_gu, self.w_d, shared, st)
+        routed = ops.moe_route(x, self.w_router, self.correction, self.top, self.groups, self.keep, bias=self.bias,
+                               extra=1 if self.shared_gate else 0)
+        ids, weights = routed[0], routed[1]
+        gate = routed[2].view(-1) if self.shared_gate else None
+        shared = None
+        if self.shared_ff:
+            shared = ops.linear(ops.linear_glu(x, self.ws_gu, status=st, act=self.shared_activation, limit=self.shared_limit),
+                                self.ws_d, status=st)
+        out = ops.moe_experts(x, ids, weights, self.w_gu, self.w_d, shared, st, act=self.activation, limit=self.limit,
+                              shared_gate=gate)
         if self.rt.trace is not None:
             self.rt.record(self._name("router.ids"), ids)
             self.rt.record(self._name("router.weights"), weights)
