@@ -4,8 +4,6 @@ time and nothing kept between calls: what the engine's kernels, caches and state
 Notation: x is the residual stream [T, width]; positions count from 0; weights are stored [out, in].
 """
 
-import math
-
 import torch
 
 F64 = torch.float64
@@ -17,10 +15,6 @@ def unit_rms(x, eps):
 
 def rms_norm(x, gain, eps):
     return unit_rms(x, eps) * gain
-
-
-def gelu_tanh(z):
-    return 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3)))
 
 
 def silu(z):
@@ -202,3 +196,8 @@ def forward(cfg, w, tokens, want_layers=False):
         streams.append(x)
     logits = (rms_norm(x, w["final.norm"], eps) @ w["head"].T) * cfg["logit_scale"]
     return (logits, torch.stack(streams)) if want_layers else logits
+
+
+def greedy(logits):
+    """The lowest index among the largest logits."""
+    return int(torch.nonzero(logits == logits.max())[0])
