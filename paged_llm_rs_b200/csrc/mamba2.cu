@@ -66,7 +66,7 @@ __global__ void __launch_bounds__(128) mamba2_conv_kernel(const T* u, int u_widt
 
 // grid (segments, heads); thread (part, e): value entry e = tid % P, state rows n = part, part + parts, ...
 template <typename T, int NPT>
-__global__ void mamba2_scan_kernel(const T* u, int u_width, int dt_off, int conv_in_off, const float* c, int channels,
+__global__ void __launch_bounds__(NPT <= 32 ? 1024 : 256) mamba2_scan_kernel(const T* u, int u_width, int dt_off, int conv_in_off, const float* c, int channels,
                                    const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
                                    const Segment* __restrict__ segs, float* state, long long state_stride, long long conv_off,
                                    float* __restrict__ y, int heads, int groups, int P, int N, int taps, int parts) {
@@ -220,13 +220,14 @@ PLLM_EXPORT int pllm_mamba2_mix(int dtype, const void* u, const void* conv_w, co
     const int u_width = 2 * inner + 2 * groups * N + heads;
     const long long conv_off = (long long)heads * N * P;
     if (state_stride < conv_off + (long long)(taps - 1) * channels) return PLLM_ERR_SIZE;
-    // threads of the scan: as many parts of P threads as fit 256 (1024 where a thread would hold more than 64 state rows)
+    // threads of the scan: as many parts of P threads as fit 256 (1024 where a thread would hold more than 64 state rows;
+    // a thread of 1024 holds 32 at most, for the registers to suffice)
     int threads = 256;
     if (P > 256 || (N + (256 / P) - 1) / (256 / P) > 64) threads = 1024;
     int parts = threads / P;
     if (parts > N) parts = N;
     const int npt = (N + parts - 1) / parts;
-    if (npt > 64) return PLLM_ERR_LIMIT;
+    if (npt > (threads == 1024 ? 32 : 64)) return PLLM_ERR_LIMIT;
     threads = (parts * P + 31) / 32 * 32;
     if (threads < M2_CHUNK) threads = 32;
     const size_t smem = ((size_t)M2_CHUNK * P + 2 * (size_t)M2_CHUNK * N + 2 * M2_CHUNK + (size_t)M2_CHUNK * parts * P) * sizeof(float);
@@ -239,7 +240,9 @@ PLLM_EXPORT int pllm_mamba2_mix(int dtype, const void* u, const void* conv_w, co
         const dim3 grid(n_segs, heads);
         const int dt_off = 2 * inner + 2 * groups * N;
         if (npt <= 4) launch_scan<T, 4>(threads, smem, grid, stream, u, u_width, dt_off, inner, c_buf, channels, dt_bias, a_log, d_skip, segs, state, state_stride, conv_off, y_buf, heads, groups, P, N, taps, parts);
+        else if (npt <= 8) launch_scan<T, 8>(threads, smem, grid, stream, u, u_width, dt_off, inner, c_buf, channels, dt_bias, a_log, d_skip, segs, state, state_stride, conv_off, y_buf, heads, groups, P, N, taps, parts);
         else if (npt <= 16) launch_scan<T, 16>(threads, smem, grid, stream, u, u_width, dt_off, inner, c_buf, channels, dt_bias, a_log, d_skip, segs, state, state_stride, conv_off, y_buf, heads, groups, P, N, taps, parts);
+        else if (npt <= 32) launch_scan<T, 32>(threads, smem, grid, stream, u, u_width, dt_off, inner, c_buf, channels, dt_bias, a_log, d_skip, segs, state, state_stride, conv_off, y_buf, heads, groups, P, N, taps, parts);
         else launch_scan<T, 64>(threads, smem, grid, stream, u, u_width, dt_off, inner, c_buf, channels, dt_bias, a_log, d_skip, segs, state, state_stride, conv_off, y_buf, heads, groups, P, N, taps, parts);
         launch_chained(mamba2_gate_norm_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, (const float*)y_buf, (const T*)u, u_width, gain,
                        (T*)out, inner, norm_groups, eps);

@@ -6,6 +6,8 @@ longer than the prompt, no kept tokens and several pages of them, rotation of a 
 convolution widths, state groups and norm groups, one expert a token and several, a shared expert and none, a layer
 without a feed-forward, models of one mixer kind only.  Weights are drawn so that attention, the recurrence and the
 routing all decide something: matrices N(0, 1 / fan_in), gains near one, sinks and biases of the size of the scores.
+The routed experts' last matrices are drawn smaller and the router's bias wider, so that a choice between two experts
+that bfloat16 rounding turns (the plain implementation is float64) moves a few positions, not most.
 """
 
 import json
@@ -109,7 +111,7 @@ def tensor_shapes(cfg):
         else:
             E = mlp["router"]["experts"]
             out[f"{p}.mlp.router"] = ((E, D), "router")
-            out[f"{p}.mlp.router.b"] = ((E,), "bias")
+            out[f"{p}.mlp.router.b"] = ((E,), "router_bias")
             for k in range(E):
                 ffn(f"{p}.mlp.e{k}", mlp["expert"]["ff"])
             if mlp.get("shared"):
@@ -128,6 +130,8 @@ def random_weights(cfg, seed):
             t = 1.0 + 0.2 * r()
         elif kind == "bias":
             t = 0.5 * r()
+        elif kind == "router_bias":
+            t = 1.5 * r()                         # (wide enough that few choices are close calls)
         elif kind == "sink":
             t = 1.0 + r()
         elif kind == "lambda":
@@ -142,6 +146,8 @@ def random_weights(cfg, seed):
             t = r()
         else:
             t = 1.3 * r() / shape[-1] ** 0.5
+            if ".mlp.e" in name and name.endswith(".down"):
+                t = 0.5 * t                       # (a close call of the router that rounding turns moves the stream by less)
         w[name] = t.to(torch.bfloat16)
     return w
 
