@@ -15,6 +15,8 @@
 //   attention_sink      the attention itself, from the step's work items (kernels/attention_plan.py): an item's rows
 //                       attend over its key range and, in the first split of a range, over the kept first tokens
 //                       before it and the sink; splits leave (max, sum, unnormalised output) for attention_reduce.
+//                       Float arithmetic on the CUDA cores, for any sizes: the true 32-bit path.
+//   attention_sink_mma  the same on the tensor cores for bfloat16 and key / value sizes of 32, 64 or 128.
 #include "common.cuh"
 
 enum : int { KID_ATT_SINK = 70 };
@@ -279,6 +281,275 @@ PLLM_EXPORT int pllm_attention_sink(int dtype, const void* q, const void* kv_poo
                        n_pages, table_width, window, keep_first, scale, cap, heads_per_cta, status);
     });
     return launch_status();
+}
+
+// ---- the same attention on the tensor cores (bfloat16) ------------------------------------------------------------
+// One CTA of four warps per (item, kv head, part of the group) holds up to 64 query rows (token x head of the group,
+// ordered as above), 16 a warp.  Keys and values come in tiles of 64 cached tokens, copied as they lie in the pages
+// (cp.async, 16 bytes a thread; rows past the range or in pages given back are zero-filled) into padded rows of shared
+// memory; S = Q K^T and O += P V are mma.sync m16n8k16 products with float accumulators, the operands fetched with
+// ldmatrix (V transposed on the way); scale, cap, mask and the running softmax act on the accumulator registers.  A warp
+// skips tiles none of its rows can see.  Key and value sizes are template parameters (32, 64 or 128 each).
+#define SMMA_BK 64
+#define SMMA_ROWS 64
+#define SMMA_PAD 8
+
+__device__ __forceinline__ uint32_t sink_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void sink_cp_async16(uint32_t dst, const void* src, bool valid) {
+    const int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void sink_cp_async_wait_all() {
+    asm volatile("cp.async.commit_group;\n" ::);
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+}
+__device__ __forceinline__ void sink_ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void sink_ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void sink_mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t sink_pack_bf16(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(128) attention_sink_mma_kernel(const bf16* q, const bf16* kv_pool, const int* __restrict__ block_tables,
+                                                                 const SinkWork* __restrict__ work, const int* __restrict__ n_work_ptr,
+                                                                 bf16* __restrict__ out, float* __restrict__ part_o,
+                                                                 float* __restrict__ part_ml, const float* __restrict__ sinks, int nh,
+                                                                 int nkv, int page_size, int n_pages, int table_width, int window,
+                                                                 int keep_first, float scale, float cap, int heads_per_cta, int* status) {
+    constexpr int QS = DK + SMMA_PAD, KS = DK + SMMA_PAD, VS = DV + SMMA_PAD;      // row strides in elements
+    extern __shared__ __align__(16) unsigned char sink_smem[];
+    bf16* q_s = reinterpret_cast<bf16*>(sink_smem);            // [SMMA_ROWS][QS]
+    bf16* k_s = q_s + SMMA_ROWS * QS;                          // [SMMA_BK][KS]
+    bf16* v_s = k_s + SMMA_BK * KS;                            // [SMMA_BK][VS]
+    __shared__ int page_s[SMMA_BK];
+    pdl_launch_dependents();
+    pdl_wait(KID_ATT_SINK);
+    if ((int)blockIdx.x >= *n_work_ptr) return;
+    const SinkWork w = work[blockIdx.x];
+    const int group = nh / nkv;
+    const int gparts = (group + heads_per_cta - 1) / heads_per_cta;
+    const int kh = blockIdx.y / gparts;
+    const int head0 = kh * group + (blockIdx.y % gparts) * heads_per_cta;
+    const int n_heads = min(heads_per_cta, kh * group + group - head0);
+    const int rows = w.q_count * n_heads;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+    const bool first_split = (w.split & 0xffff) == 0;
+    const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
+    constexpr int WROW = DK + DV;
+
+    // the queries of the CTA's rows into shared memory (rows past the item's are zeros)
+    for (int idx = threadIdx.x; idx < SMMA_ROWS * (DK / 8); idx += blockDim.x) {
+        const int r = idx / (DK / 8), c = (idx % (DK / 8)) * 8;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < rows) v = *reinterpret_cast<const uint4*>(q + ((size_t)(w.q_token0 + r / n_heads) * nh + head0 + r % n_heads) * DK + c);
+        *reinterpret_cast<uint4*>(q_s + r * QS + c) = v;
+    }
+    __syncthreads();
+    uint32_t qf[DK / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < DK / 16; kk++)
+        sink_ldmatrix_x4(qf[kk], sink_smem_u32(q_s + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * QS + kk * 16 + (lane >> 4) * 8));
+
+    // this thread's two rows: r0 = warp * 16 + g and r0 + 8
+    const int r0 = warp * 16 + g, r1 = r0 + 8;
+    const int pos0 = w.q_pos0 + (r0 < rows ? r0 / n_heads : 0), pos1 = w.q_pos0 + (r1 < rows ? r1 / n_heads : 0);
+    const bool live0 = r0 < rows, live1 = r1 < rows;
+    // positions of the warp's rows, for skipping tiles: rows warp*16 .. warp*16+15 that exist
+    const int wr_lo = warp * 16, wr_hi = min(rows, warp * 16 + 16) - 1;
+    const bool warp_live = wr_lo < rows;
+    const int wpos_lo = w.q_pos0 + wr_lo / n_heads, wpos_hi = w.q_pos0 + (warp_live ? wr_hi / n_heads : 0);
+
+    float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
+    float o[DV / 8][4];
+#pragma unroll
+    for (int j = 0; j < DV / 8; j++) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+    const int* table = block_tables + (size_t)w.seg * table_width;
+
+    for (int range = 0; range < 2; range++) {
+        const int r_begin = range == 0 ? 0 : w.kv_begin;
+        const int r_end = range == 0 ? (first_split && window > 0 ? min(keep_first, w.kv_begin) : 0) : w.kv_end;
+        for (int kv0 = r_begin; kv0 < r_end; kv0 += SMMA_BK) {
+            __syncthreads();                 // the tile before is no longer read
+            if (threadIdx.x < SMMA_BK) {
+                const int j = kv0 + threadIdx.x;
+                int page = -1;
+                if (j < r_end) {
+                    const int b = j / page_size;
+                    page = b < table_width ? table[b] : -1;
+                    if (page >= n_pages) { atomicOr(status, 8); page = -1; }
+                }
+                page_s[threadIdx.x] = page;
+            }
+            __syncthreads();
+            for (int idx = threadIdx.x; idx < SMMA_BK * (WROW / 8); idx += blockDim.x) {
+                const int j = idx / (WROW / 8), c = (idx % (WROW / 8)) * 8;
+                const int page = page_s[j];
+                const bf16* src = kv_pool + (((size_t)max(page, 0) * nkv + kh) * page_size + (kv0 + j) % page_size) * WROW + c;
+                bf16* dst = c < DK ? k_s + j * KS + c : v_s + j * VS + (c - DK);
+                sink_cp_async16(sink_smem_u32(dst), src, page >= 0);
+            }
+            sink_cp_async_wait_all();
+            __syncthreads();
+            // can any row of this warp see any key of the tile?
+            const int t_hi = min(kv0 + SMMA_BK, r_end) - 1;
+            bool any = warp_live && kv0 <= wpos_hi;
+            if (any && window > 0) any = t_hi > wpos_lo - window || kv0 < keep_first;
+            if (!any) continue;
+
+            float sc[SMMA_BK / 8][4];
+#pragma unroll
+            for (int j = 0; j < SMMA_BK / 8; j++) { sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f; }
+#pragma unroll
+            for (int kk = 0; kk < DK / 16; kk++) {
+#pragma unroll
+                for (int j = 0; j < SMMA_BK / 8; j += 2) {
+                    uint32_t b[4];
+                    sink_ldmatrix_x4(b, sink_smem_u32(k_s + (j * 8 + (lane & 7) + (lane >> 4) * 8) * KS + kk * 16 + ((lane >> 3) & 1) * 8));
+                    sink_mma_bf16(sc[j], qf[kk], b[0], b[1]);
+                    sink_mma_bf16(sc[j + 1], qf[kk], b[2], b[3]);
+                }
+            }
+            // scale, cap, mask; the tile's row maxima
+            float tm0 = -CUDART_INF_F, tm1 = -CUDART_INF_F;
+#pragma unroll
+            for (int j = 0; j < SMMA_BK / 8; j++) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int key = kv0 + j * 8 + t4 * 2 + (e & 1);
+                    const int pos = e < 2 ? pos0 : pos1;
+                    const bool live = e < 2 ? live0 : live1;
+                    const bool seen = live && key < r_end && key <= pos && (window <= 0 || pos - key < window || key < keep_first);
+                    float v = sc[j][e] * scale;
+                    if (cap > 0.f) v = cap * tanhf(v * inv_cap);
+                    v = seen ? v : -CUDART_INF_F;
+                    sc[j][e] = v;
+                    if (e < 2) tm0 = fmaxf(tm0, v); else tm1 = fmaxf(tm1, v);
+                }
+            }
+            tm0 = fmaxf(tm0, __shfl_xor_sync(0xffffffffu, tm0, 1)); tm0 = fmaxf(tm0, __shfl_xor_sync(0xffffffffu, tm0, 2));
+            tm1 = fmaxf(tm1, __shfl_xor_sync(0xffffffffu, tm1, 1)); tm1 = fmaxf(tm1, __shfl_xor_sync(0xffffffffu, tm1, 2));
+            const float mn0 = fmaxf(m0, tm0), mn1 = fmaxf(m1, tm1);
+            const float c0 = mn0 == -CUDART_INF_F ? 1.f : expf(m0 - mn0), c1 = mn1 == -CUDART_INF_F ? 1.f : expf(m1 - mn1);
+            float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+            for (int j = 0; j < SMMA_BK / 8; j++) {
+                sc[j][0] = mn0 == -CUDART_INF_F ? 0.f : expf(sc[j][0] - mn0);
+                sc[j][1] = mn0 == -CUDART_INF_F ? 0.f : expf(sc[j][1] - mn0);
+                sc[j][2] = mn1 == -CUDART_INF_F ? 0.f : expf(sc[j][2] - mn1);
+                sc[j][3] = mn1 == -CUDART_INF_F ? 0.f : expf(sc[j][3] - mn1);
+                s0 += sc[j][0] + sc[j][1];
+                s1 += sc[j][2] + sc[j][3];
+            }
+            s0 += __shfl_xor_sync(0xffffffffu, s0, 1); s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
+            s1 += __shfl_xor_sync(0xffffffffu, s1, 1); s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+            l0 = l0 * c0 + s0; l1 = l1 * c1 + s1;
+            m0 = mn0; m1 = mn1;
+#pragma unroll
+            for (int j = 0; j < DV / 8; j++) { o[j][0] *= c0; o[j][1] *= c0; o[j][2] *= c1; o[j][3] *= c1; }
+            // O += P V
+#pragma unroll
+            for (int kk = 0; kk < SMMA_BK / 16; kk++) {
+                uint32_t a[4];
+                a[0] = sink_pack_bf16(sc[2 * kk][0], sc[2 * kk][1]);
+                a[1] = sink_pack_bf16(sc[2 * kk][2], sc[2 * kk][3]);
+                a[2] = sink_pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
+                a[3] = sink_pack_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
+#pragma unroll
+                for (int j = 0; j < DV / 8; j += 2) {
+                    uint32_t b[4];
+                    sink_ldmatrix_x4_trans(b, sink_smem_u32(v_s + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VS + j * 8 + (lane >> 4) * 8));
+                    sink_mma_bf16(o[j], a, b[0], b[1]);
+                    sink_mma_bf16(o[j + 1], a, b[2], b[3]);
+                }
+            }
+        }
+    }
+    // the sink, then the rows leave
+#pragma unroll
+    for (int half = 0; half < 2; half++) {
+        const int r = half ? r1 : r0;
+        if (r >= rows) continue;
+        const int tq = r / n_heads, head = head0 + r % n_heads;
+        float m = half ? m1 : m0, l = half ? l1 : l0, corr = 1.f;
+        if (first_split && sinks) {
+            const float s = sinks[head];
+            const float mn = fmaxf(m, s);
+            corr = m == -CUDART_INF_F ? 0.f : expf(m - mn);
+            l = l * corr + expf(s - mn);
+            m = mn;
+        }
+        if (w.part_slot < 0) {
+            const float f = corr * (l > 0.f ? 1.0f / l : 0.f);
+            bf16* dst = out + ((size_t)(w.q_token0 + tq) * nh + head) * DV;
+#pragma unroll
+            for (int j = 0; j < DV / 8; j++)
+                *reinterpret_cast<uint32_t*>(dst + j * 8 + t4 * 2) = sink_pack_bf16(o[j][2 * half] * f, o[j][2 * half + 1] * f);
+        } else {
+            const size_t pr = (size_t)(w.part_slot + tq) * nh + head;
+            float* dst = part_o + pr * DV;
+#pragma unroll
+            for (int j = 0; j < DV / 8; j++) { dst[j * 8 + t4 * 2] = o[j][2 * half] * corr; dst[j * 8 + t4 * 2 + 1] = o[j][2 * half + 1] * corr; }
+            if (t4 == 0) { part_ml[pr * 2] = m; part_ml[pr * 2 + 1] = l; }
+        }
+    }
+}
+
+static inline bool sink_mma_dims(int dk, int dv) { return (dk == 32 || dk == 64 || dk == 128) && (dv == 32 || dv == 64 || dv == 128); }
+
+// Whether the tensor-core kernel takes this shape (bfloat16 only).
+PLLM_EXPORT int pllm_attention_sink_mma_supports(int dtype, int nh, int nkv, int dk, int dv) {
+    return dtype == PLLM_BF16 && nh > 0 && nkv > 0 && nh % nkv == 0 && sink_mma_dims(dk, dv);
+}
+
+PLLM_EXPORT int pllm_attention_sink_mma_tile_tokens(int nh, int nkv) {
+    const int group = nh / nkv;
+    const int heads_per_cta = group < SMMA_ROWS ? group : SMMA_ROWS;
+    return SMMA_ROWS / heads_per_cta;
+}
+
+template <int DK, int DV>
+static int launch_sink_mma(const void* q, const void* kv_pool, const int* block_tables, const int* work, const int* n_work_ptr, int max_work,
+                           void* out, float* part_o, float* part_ml, const float* sinks, int nh, int nkv, int page_size, int n_pages,
+                           int table_width, int window, int keep_first, float scale, float cap, int* status, cudaStream_t stream) {
+    const int group = nh / nkv;
+    const int heads_per_cta = group < SMMA_ROWS ? group : SMMA_ROWS;
+    const int gparts = (group + heads_per_cta - 1) / heads_per_cta;
+    const size_t smem = ((size_t)SMMA_ROWS * (DK + SMMA_PAD) + (size_t)SMMA_BK * (DK + SMMA_PAD) + (size_t)SMMA_BK * (DV + SMMA_PAD)) * sizeof(bf16);
+    cudaFuncSetAttribute(attention_sink_mma_kernel<DK, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_chained(attention_sink_mma_kernel<DK, DV>, dim3(max_work, nkv * gparts), dim3(128), smem, stream, (const bf16*)q,
+                   (const bf16*)kv_pool, block_tables, (const SinkWork*)work, n_work_ptr, (bf16*)out, part_o, part_ml, sinks, nh, nkv,
+                   page_size, n_pages, table_width, window, keep_first, scale, cap, heads_per_cta, status);
+    return launch_status();
+}
+
+PLLM_EXPORT int pllm_attention_sink_mma(const void* q, const void* kv_pool, const int* block_tables, const int* work,
+                                        const int* n_work_ptr, int max_work, void* out, float* part_o, float* part_ml,
+                                        const float* sinks, int nh, int nkv, int dk, int dv, int page_size, int n_pages, int table_width,
+                                        int window, int keep_first, float scale, float cap, int* status, cudaStream_t stream) {
+    if (max_work <= 0) return PLLM_OK;
+    if (!pllm_attention_sink_mma_supports(PLLM_BF16, nh, nkv, dk, dv) || page_size <= 0 || window < 0 || keep_first < 0) return PLLM_ERR_SIZE;
+    if (((uintptr_t)q | (uintptr_t)kv_pool) & 15) return PLLM_ERR_ALIGN;
+#define SINK_MMA_CASE(A, B)                                                                                                     \
+    if (dk == A && dv == B)                                                                                                     \
+        return launch_sink_mma<A, B>(q, kv_pool, block_tables, work, n_work_ptr, max_work, out, part_o, part_ml, sinks, nh, nkv, \
+                                     page_size, n_pages, table_width, window, keep_first, scale, cap, status, stream);
+    SINK_MMA_CASE(32, 32) SINK_MMA_CASE(32, 64) SINK_MMA_CASE(32, 128)
+    SINK_MMA_CASE(64, 32) SINK_MMA_CASE(64, 64) SINK_MMA_CASE(64, 128)
+    SINK_MMA_CASE(128, 32) SINK_MMA_CASE(128, 64) SINK_MMA_CASE(128, 128)
+#undef SINK_MMA_CASE
+    return PLLM_ERR_SIZE;
 }
 
 // The most query tokens one work item may hold for a given group size.

@@ -94,6 +94,9 @@ def lib():
         sig["pllm_rope_mix_kv_write"] = [c_int, P, c_int, P, P, c_int, P, P, P, P, c_int, P] + [c_int] * 6 + [c_ll, P, P]
         sig["pllm_attention_sink"] = [c_int, P, P, P, P, P, c_int, P, P, P, P] + [c_int] * 9 + [c_float, c_float, P, P]
         sig["pllm_attention_sink_tile_tokens"] = [c_int, c_int]
+        sig["pllm_attention_sink_mma_supports"] = [c_int] * 5
+        sig["pllm_attention_sink_mma_tile_tokens"] = [c_int, c_int]
+        sig["pllm_attention_sink_mma"] = [P, P, P, P, P, c_int, P, P, P, P] + [c_int] * 9 + [c_float, c_float, P, P]
         sig["pllm_mamba2_mix"] = [c_int] + [P] * 8 + [c_int, c_int, P, c_ll, P, P, P] + [c_int] * 7 + [c_float, P]
         sig["pllm_pack_decode_step"] = [P, c_int, c_int, P, P, P, P, P] + [c_int] * 16 + [P, P]
         for name, args in sig.items():
@@ -980,8 +983,27 @@ def rope_mix_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, inv_freq: Optional
     return q_out
 
 
-def attention_sink_tile_tokens(num_heads: int, num_kv_heads: int) -> int:
+# PAGED_LLM_SINK_MMA=0: the CUDA-core kernel everywhere (for comparisons)
+SINK_MMA = os.environ.get("PAGED_LLM_SINK_MMA", "1") != "0"
+
+
+def attention_sink_uses_tensor_cores(dtype: torch.dtype, num_heads: int, num_kv_heads: int, dk: int, dv: int) -> bool:
+    """bfloat16 with key and value sizes of 32, 64 or 128: the mma.sync kernel; everything else (and float32) runs the
+    CUDA-core kernel."""
+    return SINK_MMA and dtype == torch.bfloat16 and bool(
+        lib().pllm_attention_sink_mma_supports(_BF16, int(num_heads), int(num_kv_heads), int(dk), int(dv)))
+
+
+def attention_sink_tile_tokens(num_heads: int, num_kv_heads: int, dtype: torch.dtype = torch.float32, dk: int = 0, dv: int = 0) -> int:
+    """The most query tokens one work item of ``attention_sink`` may hold, for the kernel it picks."""
+    if attention_sink_uses_tensor_cores(dtype, num_heads, num_kv_heads, dk, dv):
+        return int(lib().pllm_attention_sink_mma_tile_tokens(int(num_heads), int(num_kv_heads)))
     return int(lib().pllm_attention_sink_tile_tokens(int(num_heads), int(num_kv_heads)))
+
+
+def attention_sink_ctas_per_item(num_heads: int, num_kv_heads: int, dtype: torch.dtype = torch.float32, dk: int = 0, dv: int = 0) -> int:
+    rows = 64 if attention_sink_uses_tensor_cores(dtype, num_heads, num_kv_heads, dk, dv) else 16
+    return num_kv_heads * -(-(num_heads // num_kv_heads) // rows)
 
 
 def attention_sink(q: torch.Tensor, kv_pool: torch.Tensor, block_tables: torch.Tensor, w, out: torch.Tensor,
@@ -1010,10 +1032,16 @@ def attention_sink(q: torch.Tensor, kv_pool: torch.Tensor, block_tables: torch.T
         raise KernelError("attention_sink: work / red lists shorter than their maxima")
     n_pages, page_size = kv_pool.shape[0], kv_pool.shape[2]
     L = lib()
-    _check(L.pllm_attention_sink(_code(q), _ptr(q), _ptr(kv_pool), _ptr(block_tables), _ptr(work), _ptr(n_work), max_work, _ptr(out),
-                                 _ptr(part_o), _ptr(part_ml), _ptr(sinks), num_heads, num_kv_heads, dk, dv, page_size, n_pages,
-                                 block_tables.shape[-1], int(window), int(keep_first), float(scale), float(cap), _ptr(status),
-                                 _stream()), "attention_sink")
+    if attention_sink_uses_tensor_cores(q.dtype, num_heads, num_kv_heads, dk, dv):
+        _check(L.pllm_attention_sink_mma(_ptr(q), _ptr(kv_pool), _ptr(block_tables), _ptr(work), _ptr(n_work), max_work, _ptr(out),
+                                         _ptr(part_o), _ptr(part_ml), _ptr(sinks), num_heads, num_kv_heads, dk, dv, page_size, n_pages,
+                                         block_tables.shape[-1], int(window), int(keep_first), float(scale), float(cap), _ptr(status),
+                                         _stream()), "attention_sink (mma)")
+    else:
+        _check(L.pllm_attention_sink(_code(q), _ptr(q), _ptr(kv_pool), _ptr(block_tables), _ptr(work), _ptr(n_work), max_work,
+                                     _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(sinks), num_heads, num_kv_heads, dk, dv, page_size,
+                                     n_pages, block_tables.shape[-1], int(window), int(keep_first), float(scale), float(cap),
+                                     _ptr(status), _stream()), "attention_sink")
     _check(L.pllm_attention_reduce(_code(q), _ptr(part_o), _ptr(part_ml), _ptr(red), _ptr(n_red), max_red, _ptr(out), num_heads, dv,
                                    1 if (w.many_splits and dv * 4 <= 1024) else 0, _stream()), "attention_reduce")
     return out

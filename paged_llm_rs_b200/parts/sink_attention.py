@@ -87,8 +87,8 @@ class SinkWindowAttention(Mixer):
         return self._need
 
     def plan_wish(self, page_size: int):
-        group = self.nh // self.nkv
-        return PlanWish(ops.attention_sink_tile_tokens(self.nh, self.nkv), self.nkv * -(-group // 16), self.nh, self.dv)
+        a = (self.nh, self.nkv, self.rt.dtype, self.dk, self.dv)
+        return PlanWish(ops.attention_sink_tile_tokens(*a), ops.attention_sink_ctas_per_item(*a), self.nh, self.dv)
 
     def forward(self, x, step, cache, writes_cache=True):
         kv_pool, gi = cache

@@ -6,8 +6,11 @@ longer than the prompt, no kept tokens and several pages of them, rotation of a 
 convolution widths, state groups and norm groups, one expert a token and several, a shared expert and none, a layer
 without a feed-forward, models of one mixer kind only.  Weights are drawn so that attention, the recurrence and the
 routing all decide something: matrices N(0, 1 / fan_in), gains near one, sinks and biases of the size of the scores.
-The routed experts' last matrices are drawn smaller and the router's bias wider, so that a choice between two experts
-that bfloat16 rounding turns (the plain implementation is float64) moves a few positions, not most.
+With ``calm_router`` the router's matrix is drawn small and its bias holds well separated values: every token then takes
+the same experts by a wide margin.  Whole models in bfloat16 are compared with those weights, because rounding turns a
+router's close call about once in a hundred tokens (the plain implementation is float64), which moves that token's
+logits, and through caches and states those behind it, by far more than rounding does; the float32 comparisons and the
+router's own test use routers that decide token by token.
 """
 
 import json
@@ -120,7 +123,7 @@ def tensor_shapes(cfg):
     return out
 
 
-def random_weights(cfg, seed):
+def random_weights(cfg, seed, calm_router=False):
     """bfloat16 tensors (what a model file holds)."""
     g = torch.Generator().manual_seed(seed)
     w = {}
@@ -131,7 +134,7 @@ def random_weights(cfg, seed):
         elif kind == "bias":
             t = 0.5 * r()
         elif kind == "router_bias":
-            t = 1.5 * r()                         # (wide enough that few choices are close calls)
+            t = 0.8 * torch.randperm(shape[0], generator=g).float() if calm_router else 0.5 * r()
         elif kind == "sink":
             t = 1.0 + r()
         elif kind == "lambda":
@@ -141,24 +144,22 @@ def random_weights(cfg, seed):
         elif kind == "conv":
             t = 0.6 * r()
         elif kind == "router":
-            t = 2.0 * r() / shape[-1] ** 0.5
+            t = (0.05 if calm_router and name.endswith(".router") else 2.0) * r() / shape[-1] ** 0.5
         elif kind == "table":
             t = r()
         else:
             t = 1.3 * r() / shape[-1] ** 0.5
-            if ".mlp.e" in name and name.endswith(".down"):
-                t = 0.5 * t                       # (a close call of the router that rounding turns moves the stream by less)
         w[name] = t.to(torch.bfloat16)
     return w
 
 
-def write_model(folder, name, seed=0, cfg=None):
+def write_model(folder, name, seed=0, cfg=None, calm_router=False):
     """A model folder for configuration ``name``; returns (folder, config dict, float64 weights for the plain implementation)."""
     from paged_llm_rs_b200.weights.safetensors_io import write_safetensors
 
     cfg = cfg or CONFIGS[name]
-    w = random_weights(cfg, seed)
-    d = os.path.join(str(folder), f"bumisun_{name}_{seed}")
+    w = random_weights(cfg, seed, calm_router)
+    d = os.path.join(str(folder), f"bumisun_{name}_{seed}{'_calm' if calm_router else ''}")
     os.makedirs(d, exist_ok=True)
     with open(os.path.join(d, "config.json"), "w") as f:
         json.dump(cfg, f)

@@ -206,7 +206,7 @@ def run_attention(dtype, reqs, nh, nkv, dk, dv, page, window, keep, cap, scale=N
     g = gen(5)
     scale = scale if scale is not None else 1.0 / dk ** 0.5
     group = nh // nkv
-    tile, ctas = ops.attention_sink_tile_tokens(nh, nkv), nkv * -(-group // 16)
+    tile, ctas = ops.attention_sink_tile_tokens(nh, nkv, dtype, dk, dv), ops.attention_sink_ctas_per_item(nh, nkv, dtype, dk, dv)
     total_pages = sum(-(-(c + n) // page) for c, n in reqs) + 3
     order = torch.randperm(total_pages, generator=g).tolist()
     pool = torch.zeros(total_pages, nkv, page, dk + dv)
@@ -257,7 +257,8 @@ def run_attention(dtype, reqs, nh, nkv, dk, dv, page, window, keep, cap, scale=N
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh,nkv,dk,dv,page,window,keep,cap", [
     (6, 2, 16, 8, 16, 20, 3, 20.0), (5, 1, 12, 20, 8, 9, 21, 0.0), (8, 2, 128, 64, 16, 40, 4, 30.0), (20, 1, 32, 32, 16, 500, 4, 5.0),
-    (4, 4, 24, 16, 4, 33, 0, 2.0), (3, 3, 16, 16, 16, 7, 2, 50.0), (8, 2, 64, 64, 32, 128, 16, 30.0), (2, 1, 256, 256, 16, 0, 0, 0.0)])
+    (4, 4, 24, 16, 4, 33, 0, 2.0), (3, 3, 16, 16, 16, 7, 2, 50.0), (8, 2, 64, 64, 32, 128, 16, 30.0), (2, 1, 256, 256, 16, 0, 0, 0.0),
+    (64, 8, 64, 64, 16, 128, 0, 0.0), (10, 2, 32, 128, 8, 70, 9, 10.0), (80, 1, 64, 32, 16, 30, 2, 0.0), (3, 3, 128, 128, 16, 100, 65, 30.0)])
 def test_attention_mixed_batch(dtype, nh, nkv, dk, dv, page, window, keep, cap):
     reqs = [(0, 1), (0, 37), (130, 1), (63, 2), (64, 5), (200, 1), (15, 17), (0, 2), (300, 40)]
     res, _ = run_attention(dtype, reqs, nh, nkv, dk, dv, page, window, keep, cap)
@@ -412,13 +413,12 @@ TOL = {torch.float32: 2e-4, torch.bfloat16: 6e-2}
 
 
 def agrees(got, want, dtype):
-    """float32: every position within rounding.  bfloat16: rounding turns a router's close call now and then (about one
-    token in a hundred of these models), which moves that token's logits by more than rounding does and, through the
-    mixers' caches and states, those of the tokens behind it a little: most positions must be well within, none far out."""
+    """float32: every position within rounding.  bfloat16 (models whose routers do not decide by close calls, see
+    bumisun_models.py): most positions well within, a few may be out, none far."""
     e = errors(got, want)
     if dtype == torch.float32:
         return float(e.max()) < TOL[dtype]
-    return float(e.median()) < 0.5 * TOL[dtype] and float((e > TOL[dtype]).double().mean()) <= 0.35 and float(e.max()) < 0.6
+    return float(e.median()) < 0.5 * TOL[dtype] and float((e > TOL[dtype]).double().mean()) <= 0.1 and float(e.max()) < 0.3
 
 
 def stream_agrees(got, want, dtype, what):
@@ -436,10 +436,11 @@ _models = {}
 def models(tmp_path_factory):
     root = tmp_path_factory.mktemp("bumisun")
 
-    def get(name):
-        if name not in _models:
-            _models[name] = write_model(root, name, seed=len(_models))
-        return _models[name]
+    def get(name, dtype):
+        calm = dtype == torch.bfloat16
+        if (name, calm) not in _models:
+            _models[(name, calm)] = write_model(root, name, seed=len(_models), calm_router=calm)
+        return _models[(name, calm)]
     return get
 
 
@@ -450,7 +451,7 @@ def tokens_for(cfg, n, seed):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", sorted(CONFIGS))
 def test_whole_prompt_and_every_layer(models, dtype, name):
-    folder, cfg, w = models(name)
+    folder, cfg, w = models(name, dtype)
     toks = tokens_for(cfg, 45, 1)
     want, streams = P.forward(cfg, w, toks, want_layers=True)
     s = Served(folder, dtype)
@@ -468,7 +469,7 @@ def test_whole_prompt_and_every_layer(models, dtype, name):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name,page", [("small", 16), ("odd", 8), ("wide", 32), ("state_only", 16), ("attention_only", 4)])
 def test_prefill_against_token_by_token_decoding(models, dtype, name, page):
-    folder, cfg, w = models(name)
+    folder, cfg, w = models(name, dtype)
     toks = tokens_for(cfg, 70, 2)
     want = P.forward(cfg, w, toks)
     s = Served(folder, dtype, page=page, pages=40)
@@ -482,7 +483,7 @@ def test_prefill_against_token_by_token_decoding(models, dtype, name, page):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["small", "odd", "wide"])
 def test_portions_of_every_size(models, dtype, name):
-    folder, cfg, w = models(name)
+    folder, cfg, w = models(name, dtype)
     toks = tokens_for(cfg, 150, 3)
     want = P.forward(cfg, w, toks)
     for cuts in ([2] * 10 + [3, 5, 16, 17, 31, 33, 25], [64, 64, 22], [1, 2, 13, 48, 1, 1, 84], [149, 1]):
@@ -500,7 +501,7 @@ def test_portions_of_every_size(models, dtype, name):
 def test_batches_of_unequal_requests_pages_and_slots_used_again(models, dtype, name):
     """Four live requests, portions beside single tokens, in a pool and with state slots that only hold them if those
     of finished requests are used again; every row against the plain implementation of its request alone."""
-    folder, cfg, w = models(name)
+    folder, cfg, w = models(name, dtype)
     lengths = dict(a=90, b=33, c=7, d=64, e=50, f=21)
     toks = {k: tokens_for(cfg, n, 10 + i) for i, (k, n) in enumerate(lengths.items())}
     want = {k: P.forward(cfg, w, t) for k, t in toks.items()}
@@ -525,7 +526,7 @@ def test_batches_of_unequal_requests_pages_and_slots_used_again(models, dtype, n
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name,page", [("small", 8), ("odd", 4)])
 def test_long_decoding_while_windows_pass_and_pages_go_back(models, dtype, name, page):
-    folder, cfg, w = models(name)
+    folder, cfg, w = models(name, dtype)
     toks = tokens_for(cfg, 330, 5)
     want = P.forward(cfg, w, toks)
     s = Served(folder, dtype, page=page, pages=30)        # fewer pages than 330 tokens need: the windows' pages are used again
@@ -537,7 +538,7 @@ def test_long_decoding_while_windows_pass_and_pages_go_back(models, dtype, name,
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_a_request_left_out_of_steps_goes_on_later(models, dtype):
-    folder, cfg, w = models("small")
+    folder, cfg, w = models("small", dtype)
     ta, tb = tokens_for(cfg, 60, 8), tokens_for(cfg, 40, 9)
     wa, wb = P.forward(cfg, w, ta), P.forward(cfg, w, tb)
     s = Served(folder, dtype)
@@ -555,7 +556,7 @@ def test_greedy_generation_through_the_scheduler(models, dtype, name):
     """Engine.generate: chunked prompts, captured decode steps, several requests at once; every produced token
     against the plain implementation on the same history."""
     from paged_llm_rs_b200 import Engine
-    folder, cfg, w = models(name)
+    folder, cfg, w = models(name, dtype)
     prompts = [tokens_for(cfg, n, 20 + n) for n in (3, 41, 18, 70, 1)]
     eng = Engine(folder, dtype=NAMES[dtype], block_size=16, blocks=64, max_batch=4, chunk=32, prefix_cache=False)
     outs = eng.generate(prompts, max_tokens=12)
@@ -577,7 +578,7 @@ def test_greedy_generation_through_the_scheduler(models, dtype, name):
 
 
 def test_trace_replay_and_command_line(models, tmp_path):
-    folder, cfg, w = models("small")
+    folder, cfg, w = models("small", torch.float32)
     from trace_tools import TraceBuilder, replay
     toks = tokens_for(cfg, 60, 7)
     tb = TraceBuilder()
@@ -646,10 +647,10 @@ def random_configuration(seed):
 @pytest.mark.parametrize("seed", list(range(1, 15)))
 def test_configurations_drawn_at_random(tmp_path, seed):
     cfg = random_configuration(seed)
-    folder, cfg, w = write_model(tmp_path, f"random{seed}", seed=seed, cfg=cfg)
     toks = tokens_for(cfg, 130, seed)
-    want = P.forward(cfg, w, toks)
     for dtype in DTYPES:
+        folder, cfg, w = write_model(tmp_path, f"random{seed}", seed=seed, cfg=cfg, calm_router=dtype == torch.bfloat16)
+        want = P.forward(cfg, w, toks)
         s = Served(folder, dtype, page=16, pages=24)
         whole = s.step([("w", toks, list(range(130)))])
         s.end("w")
