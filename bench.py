@@ -574,6 +574,186 @@ def latent_beside_dense(size, layers, pk, clocks, steps, warmup, prefill_only=Fa
     return out
 
 
+# ---- the windowed-attention / state-space / clamped-experts decoder (Bumisun) beside the grouped-query dense one ------
+# Sizes that resemble real layers: the widths of the 0.6B and of a 2B-class shape; attention of sixteen heads over eight
+# kv heads, keys of 128 and values of 64 entries, a window of 1024 tokens that keeps the first four, half of each head
+# rotated; Mamba-2 layers of width / 32 heads of 64 with a state of 128 rows; layers alternate a state-space mixer with
+# a dense gated feed-forward and an attention mixer with routed experts that together are as wide as the dense one.
+HYBRID_SIZES = {
+    "1024": dict(width=1024, heads=16, kv_heads=8, dim=128, vdim=64, window=1024, keep_first=4, rot=64, m_heads=32, m_vdim=64,
+                 m_state=128, m_groups=1, conv=4, ff=3072, experts=16, top=4, expert_ff=768, shared_ff=768),
+    "2048": dict(width=2048, heads=16, kv_heads=8, dim=128, vdim=64, window=1024, keep_first=4, rot=64, m_heads=64, m_vdim=64,
+                 m_state=128, m_groups=1, conv=4, ff=6144, experts=32, top=4, expert_ff=1536, shared_ff=1536),
+}
+
+
+def hybrid_config(z, layers):
+    att = dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["dim"], vdim=z["vdim"], scale=z["dim"] ** -0.5, softcap=30.0,
+               mask=dict(size=z["window"], keep_first=z["keep_first"]), rot=dict(dims=z["rot"], base=10000.0), v_mix=True)
+    ssm = dict(heads=z["m_heads"], vdim=z["m_vdim"], state=z["m_state"], groups=z["m_groups"], conv=z["conv"], norm_groups=1)
+    dense = dict(kind="dense", ff=z["ff"])
+    moe = dict(kind="moe", expert=dict(ff=z["expert_ff"], limit=7.0), shared=dict(ff=z["shared_ff"], limit=7.0),
+               router=dict(experts=z["experts"], top=z["top"]))
+    return dict(architecture="Bumisun", vocab=LATENT_VOCAB, width=z["width"], norm=dict(eps=1e-6), residual_mult=0.7, logit_scale=0.5,
+                layers=[dict(type="mamba2", mixer=ssm, mlp=dense) if i % 2 == 0 else dict(type="attention", mixer=att, mlp=moe)
+                        for i in range(layers)])
+
+
+def hybrid_beside_dense(size, layers, pk, clocks, steps, warmup, which="both"):
+    """Decode (batch 1, 8, 64 at context 4096) and the 2048-token prefill of the Bumisun shape ``size`` and of the Qwen3
+    shape of the same width, heads, kv heads, feed-forward width, layers and vocabulary: tokens a second, side by side."""
+    import gc
+    import torch
+    from paged_llm_rs_b200 import Engine, write_random_model
+
+    z = HYBRID_SIZES[size]
+    qwen = dict(SHAPE_0_6B, hidden_size=z["width"], intermediate_size=z["ff"], num_hidden_layers=layers,
+                num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"], head_dim=z["dim"], vocab_size=LATENT_VOCAB,
+                tie_word_embeddings=False)
+    out = dict(size=size, layers=layers, vocab=LATENT_VOCAB, hybrid=dict(z))
+    for name, cfg in (("bumisun", hybrid_config(z, layers)), ("qwen3", qwen)):
+        if which not in ("both", name):
+            continue
+        tmp = tempfile.mkdtemp(prefix="pllm_bench_", dir=scratch_dir())
+        try:
+            model_dir = write_random_model(os.path.join(tmp, "model"), cfg, 0, device="cuda")
+            ctx = 4096
+            pages = 64 * (ctx // PAGE + 4) + (PREFILL_TOKENS + 1024) // PAGE + 64
+            eng = Engine(model_dir, dtype="bfloat16", block_size=PAGE, blocks=pages, max_batch=64, chunk=PREFILL_TOKENS,
+                         prefix_cache=False)
+            shutil.rmtree(tmp, ignore_errors=True)
+            runner = eng.runner
+            for g in runner.cache.groups:
+                g.pool.normal_(0.0, 1.0)
+            res = dict(weight_bytes=runner.weight_bytes(), cache_bytes_a_token=runner.cache.bytes_per_token())
+            for b in (1, 8, 64):
+                ms, launches, spread = decode_point(runner, b, ctx, max(5, steps // 2), warmup, clocks, repeats=4)
+                res[f"decode_b{b}_tok_s"] = round(b / (spread["median_ms"] / 1e3), 1)
+                res[f"decode_b{b}_ms"] = spread["median_ms"]
+                res[f"decode_b{b}_launches"] = launches
+            pms, _ = prefill_point(runner, LATENT_VOCAB, clocks, repeats=4)
+            res["prefill_ms"] = round(pms, 3)
+            res["prefill_tok_s"] = round(PREFILL_TOKENS / (pms / 1e3), 1)
+            out[name] = res
+            del eng, runner
+        finally:
+            shutil.rmtree(tmp, ignore_errors=True)
+            gc.collect()
+            torch.cuda.empty_cache()
+    out["kernels"] = hybrid_kernels(HYBRID_SIZES[size], pk)
+    return out
+
+
+def hybrid_kernels(z, pk):
+    """Bumisun's own kernels alone, at the sizes of ``z``, beside the like kernels of the grouped-query dense model:
+    device time (CUDA events, the median of nine after three warm-ups, the cache pools larger than L2), the algorithmic
+    bytes and FLOPs, and the fraction of the measured copy bandwidth or bfloat16 product rate they come to."""
+    import numpy as np
+    import torch
+    from paged_llm_rs_b200.kernels import attention_plan, ops
+    from paged_llm_rs_b200.parts.base import AttentionWork
+
+    dev, bf = "cuda", torch.bfloat16
+    nh, nkv, dk, dv, W, keep = z["heads"], z["kv_heads"], z["dim"], z["vdim"], z["window"], z["keep_first"]
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    target = 2 * ops.sm_count()
+    out = {}
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(9):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return statistics.median(ts)
+
+    def note(name, ms, nbytes, flops):
+        r = dict(us=round(ms * 1e3, 2), mbytes=round(nbytes / 1e6, 2), gflop=round(flops / 1e9, 3),
+                 hbm_frac=round(nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4),
+                 bf16_frac=round(flops / (ms / 1e3) / 1e12 / pk["bf16_tflops"], 4))
+        r["frac_of_slower_bound"] = round(max(r["hbm_frac"], r["bf16_frac"]), 4)
+        out[name] = r
+
+    def plan(segs, tile, ctas, window):
+        work, red, parts = attention_plan.plan_attention(segs, tile, window, ctas, target)
+        wd = torch.from_numpy(np.ascontiguousarray(work)).reshape(-1, 8).to(dev) if len(work) else torch.zeros(1, 8, dtype=torch.int32, device=dev)
+        rd = torch.from_numpy(np.ascontiguousarray(red)).reshape(-1, 4).to(dev) if len(red) else torch.zeros(1, 4, dtype=torch.int32, device=dev)
+        singles = all(n == 1 for _, n, _ in segs)
+        return lambda heads, hd: AttentionWork(wd, torch.tensor([len(work)], dtype=torch.int32, device=dev), max(len(work), 1), rd,
+                                                torch.tensor([len(red)], dtype=torch.int32, device=dev), len(red),
+                                                torch.zeros(max(parts, 1), heads, hd, device=dev), torch.zeros(max(parts, 1), heads, 2, device=dev),
+                                                kinds=1 if singles else 2, many_splits=attention_plan.many_splits(len(segs), ctas, target))
+
+    ctx, B, T = 4096, 64, PREFILL_TOKENS
+    n_pages = B * ctx // PAGE
+    tables = torch.randperm(n_pages, dtype=torch.int32).view(B, ctx // PAGE).to(dev)
+    cases = {"decode_b64_ctx4096": [(i, 1, ctx - 1) for i in range(B)], "prefill_2048": [(0, T, 0)]}
+    # -- attention: capped, windowed, with sinks, joined rows (this design) and plain grouped-query with the same window (Qwen3's)
+    pool = torch.randn(n_pages, nkv, PAGE, dk + dv, device=dev).to(bf)
+    kp, vp = (torch.randn(n_pages, nkv, PAGE, dk, device=dev).to(bf) for _ in range(2))
+    swz = ops.pool_is_swizzled(bf, nh, nkv, dk)
+    sinks = torch.zeros(nh, device=dev)
+    for case, segs in cases.items():
+        n = sum(c for _, c, _ in segs)
+        keys = sum(min(p + i + 1, W) + min(keep, max(0, p + i + 1 - W)) for _, c, p in segs for i in range(c))
+        q, o = torch.randn(n, nh * dk, device=dev).to(bf), torch.empty(n, nh * dv, dtype=bf, device=dev)
+        w = plan(segs, ops.attention_sink_tile_tokens(nh, nkv, bf, dk, dv), ops.attention_sink_ctas_per_item(nh, nkv, bf, dk, dv), W)(nh, dv)
+        ms = timed(lambda: ops.attention_sink(q, pool, tables, w, o, sinks, nh, nkv, dk, dv, W, keep, dk ** -0.5, 30.0, status))
+        seg_keys = sum(min(p + c, W + c) for _, c, p in segs)            # cache rows a segment's queries read, once
+        note(f"attention_sink_{case}", ms, seg_keys * nkv * (dk + dv) * 2 + n * nh * (dk + dv) * 2, 2 * nh * (dk + dv) * keys)
+        o2 = torch.empty(n, nh * dk, dtype=bf, device=dev)
+        w2 = plan(segs, ops.attention_tile_tokens(nh, nkv, bf, dk, PAGE, W), nkv * -(-(nh // nkv) // 16), W)(nh, dk)
+        keys2 = sum(min(p + i + 1, W) for _, c, p in segs for i in range(c))
+        ms = timed(lambda: ops.paged_attention(q, kp, vp, tables, w2, o2, nh, nkv, dk, W, dk ** -0.5, status, swizzled=swz))
+        note(f"qwen3_attention_window_{case}", ms, seg_keys * nkv * 2 * dk * 2 + n * nh * 2 * dk * 2, 2 * nh * 2 * dk * keys2)
+    # -- rotation and the cache write
+    for case, n in (("decode_b64", B), ("prefill_2048", T)):
+        pos = torch.arange(n, dtype=torch.int32, device=dev)
+        slots = torch.randperm(n_pages * PAGE, dtype=torch.int32)[:n].to(dev)
+        qkv = torch.randn(n, nh * dk + nkv * (dk + dv), device=dev).to(bf)
+        q = torch.empty(n, nh * dk, dtype=bf, device=dev)
+        inv = torch.rand(z["rot"] // 2, device=dev)
+        vf, lam = torch.randn(n, nkv * dv, device=dev).to(bf), torch.tensor([0.5], device=dev)
+        ms = timed(lambda: ops.rope_mix_kv_write(qkv, q, inv, z["rot"], pos, slots, pool, vf, lam, nh, nkv, dk, dv, status))
+        note(f"rope_mix_kv_write_{case}", ms, 2 * qkv.numel() * 2 + vf.numel() * 2, 0)
+        qkv2 = torch.randn(n, (nh + 2 * nkv) * dk, device=dev).to(bf)
+        g1 = torch.ones(dk, device=dev)
+        cos, sin = torch.rand(ctx, dk // 2, device=dev), torch.rand(ctx, dk // 2, device=dev)
+        ms = timed(lambda: ops.qk_norm_rope_kv(qkv2, q, g1, g1, 1e-6, cos, sin, dk, pos, slots, kp, vp, nh, nkv, dk, status, swizzled=swz))
+        note(f"qwen3_qk_norm_rope_kv_{case}", ms, 2 * qkv2.numel() * 2, 0)
+    # -- the add before a norm, on a float32 stream and on a bfloat16 one
+    for case, n in (("decode_b64", B), ("prefill_2048", T)):
+        x32, d = torch.randn(n, z["width"], device=dev), torch.randn(n, z["width"], device=dev).to(bf)
+        g1, y = torch.ones(z["width"], device=dev), torch.empty(n, z["width"], dtype=bf, device=dev)
+        ms = timed(lambda: ops.add_scaled_norm32(x32, d, 0.7, g1, 1e-6, y))
+        note(f"add_scaled_norm32_{case}", ms, n * z["width"] * (4 + 4 + 2 + 2), 0)
+        x16 = x32.to(bf)
+        ms = timed(lambda: ops.rmsnorm(x16, g1, 1e-6, y, delta=d, residual_out=x16))
+        note(f"qwen3_add_rmsnorm_{case}", ms, n * z["width"] * (2 + 2 + 2 + 2), 0)
+    # -- the state-space mixer between its projections (no like kernel in the other models)
+    H, P_, N, G, taps = z["m_heads"], z["m_vdim"], z["m_state"], z["m_groups"], z["conv"]
+    inner, ch = H * P_, H * P_ + 2 * G * N
+    floats = ops.mamba2_state_floats(H, G, P_, N, taps)
+    state = torch.zeros(B + 1, floats, device=dev)
+    cw, cb = torch.randn(ch, taps, device=dev).to(bf), torch.randn(ch, device=dev).to(bf)
+    hb, gain = torch.zeros(H, device=dev), torch.ones(inner, device=dev)
+    for case, segs in cases.items():
+        n = sum(c for _, c, _ in segs)
+        u = torch.randn(n, inner + ch + H, device=dev).to(bf)
+        sg = torch.tensor([(t0, c, p, i + 1) for i, (t0, c, p) in enumerate(segs)], dtype=torch.int32, device=dev)
+        if len(segs) > 1:
+            sg[:, 0] = torch.arange(len(segs), dtype=torch.int32, device=dev)
+        y = torch.empty(n, inner, dtype=bf, device=dev)
+        ms = timed(lambda: ops.mamba2_mix(u, cw, cb, hb, hb, hb, gain, sg, n, state, y, H, G, P_, N, taps, 1, 1e-6))
+        nbytes = u.numel() * 2 * 2 + n * ch * 4 * 2 + n * inner * 4 * 2 + y.numel() * 2 + len(segs) * floats * 4 * 2
+        note(f"mamba2_mix_{case}", ms, nbytes, 6 * n * H * N * P_)
+    return out
+
+
 TRACE_KERNELS = {0: "(tcgen05 kernel)", 1: "embed", 2: "rmsnorm", 3: "swiglu", 4: "qk_norm_rope_kv", 5: "attention_generic", 6: "attention_reduce",
                  7: "attention_mma", 8: "attention_tma", 9: "skinny_gemm", 10: "sample_partial", 11: "sample_final", 12: "gemm_tcgen05", 13: "attention_tcgen05"}
 TRACE_FILES = ["elementwise", "qk_norm_rope_kv", "attention_generic", "attention_mma", "attention_decode_tma", "sampling",
@@ -728,14 +908,19 @@ def main(argv=None) -> int:
                     help="with --only latent: the width of the latent-attention / mixture-of-experts shape")
     ap.add_argument("--latent-part", choices=["all", "decode", "prefill"], default="all", help="with --only latent: one part alone")
     ap.add_argument("--latent-model", choices=["both", "surelorn", "qwen3"], default="both", help="with --only latent: one model alone")
-    ap.add_argument("--only", choices=["decode", "prefill", "long-prompt", "timeline", "reference-kernel", "plain-cpu", "latent"], default=None,
+    ap.add_argument("--hybrid-size", choices=sorted(HYBRID_SIZES), default="1024",
+                    help="with --only hybrid: the width of the windowed-attention / state-space / clamped-experts decoder")
+    ap.add_argument("--hybrid-model", choices=["both", "bumisun", "qwen3"], default="both", help="with --only hybrid: one model alone")
+    ap.add_argument("--only", choices=["decode", "prefill", "long-prompt", "timeline", "reference-kernel", "plain-cpu", "latent", "hybrid"], default=None,
                     help="run one part alone and print a short line (for profiling; not a bench record); "
                          "long-prompt: a prompt of --context tokens in portions of 2048, each portion timed; "
                          "timeline: one captured decode step as the kernels themselves clocked it; reference-kernel: "
                          "the reference's CUDA kernel against this engine's decode attention; plain-cpu: the plain "
                          "float32 implementation timed on the CPU (needs no GPU); latent: decode and prefill of the "
                          "latent-attention / mixture-of-experts decoder (Surelorn) beside the Qwen3 shape of equal size "
-                         "(--latent-size, --layers, default 8)")
+                         "(--latent-size, --layers, default 8); hybrid: the same for the windowed-attention / state-space / "
+                         "clamped-experts decoder (Bumisun), with its own kernels timed alone beside the like kernels of the "
+                         "Qwen3 shape (--hybrid-size, --layers, default 8)")
     args = ap.parse_args(argv)
 
     if args.impl == "reference":
@@ -765,6 +950,12 @@ def main(argv=None) -> int:
         out = latent_beside_dense(args.latent_size, args.layers or 8, pk, clocks, steps, warmup,
                                   prefill_only=args.latent_part == "prefill", decode_only=args.latent_part == "decode",
                                   which=args.latent_model)
+        out["clocks"] = clocks.stop()
+        print(json.dumps(out))
+        return 0
+    if args.only == "hybrid":
+        clocks.start()
+        out = hybrid_beside_dense(args.hybrid_size, args.layers or 8, pk, clocks, steps, warmup, which=args.hybrid_model)
         out["clocks"] = clocks.stop()
         print(json.dumps(out))
         return 0
