@@ -432,7 +432,9 @@ __global__ void __launch_bounds__(128) attention_sink_mma_kernel(const bf16* q, 
                     const bool live = e < 2 ? live0 : live1;
                     const bool seen = live && key < r_end && key <= pos && (window <= 0 || pos - key < window || key < keep_first);
                     float v = sc[j][e] * scale;
-                    if (cap > 0.f) v = cap * tanhf(v * inv_cap);
+                    // tanh(x) = 1 - 2 / (exp(2x) + 1) with the fast exponential and division: its absolute error (1e-7) is far
+                    // below what the bfloat16 operands leave in the score
+                    if (cap > 0.f) v = cap * (1.0f - __fdividef(2.0f, __expf(2.0f * v * inv_cap) + 1.0f));
                     v = seen ? v : -CUDART_INF_F;
                     sc[j][e] = v;
                     if (e < 2) tm0 = fmaxf(tm0, v); else tm1 = fmaxf(tm1, v);
@@ -441,14 +443,14 @@ __global__ void __launch_bounds__(128) attention_sink_mma_kernel(const bf16* q, 
             tm0 = fmaxf(tm0, __shfl_xor_sync(0xffffffffu, tm0, 1)); tm0 = fmaxf(tm0, __shfl_xor_sync(0xffffffffu, tm0, 2));
             tm1 = fmaxf(tm1, __shfl_xor_sync(0xffffffffu, tm1, 1)); tm1 = fmaxf(tm1, __shfl_xor_sync(0xffffffffu, tm1, 2));
             const float mn0 = fmaxf(m0, tm0), mn1 = fmaxf(m1, tm1);
-            const float c0 = mn0 == -CUDART_INF_F ? 1.f : expf(m0 - mn0), c1 = mn1 == -CUDART_INF_F ? 1.f : expf(m1 - mn1);
+            const float c0 = mn0 == -CUDART_INF_F ? 1.f : __expf(m0 - mn0), c1 = mn1 == -CUDART_INF_F ? 1.f : __expf(m1 - mn1);
             float s0 = 0.f, s1 = 0.f;
 #pragma unroll
             for (int j = 0; j < SMMA_BK / 8; j++) {
-                sc[j][0] = mn0 == -CUDART_INF_F ? 0.f : expf(sc[j][0] - mn0);
-                sc[j][1] = mn0 == -CUDART_INF_F ? 0.f : expf(sc[j][1] - mn0);
-                sc[j][2] = mn1 == -CUDART_INF_F ? 0.f : expf(sc[j][2] - mn1);
-                sc[j][3] = mn1 == -CUDART_INF_F ? 0.f : expf(sc[j][3] - mn1);
+                sc[j][0] = mn0 == -CUDART_INF_F ? 0.f : __expf(sc[j][0] - mn0);
+                sc[j][1] = mn0 == -CUDART_INF_F ? 0.f : __expf(sc[j][1] - mn0);
+                sc[j][2] = mn1 == -CUDART_INF_F ? 0.f : __expf(sc[j][2] - mn1);
+                sc[j][3] = mn1 == -CUDART_INF_F ? 0.f : __expf(sc[j][3] - mn1);
                 s0 += sc[j][0] + sc[j][1];
                 s1 += sc[j][2] + sc[j][3];
             }

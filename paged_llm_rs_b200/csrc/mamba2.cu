@@ -22,7 +22,7 @@
 enum : int { KID_MAMBA2 = 80 };
 
 #define M2_CONV_TOKENS 64      // tokens a CTA of the convolution
-#define M2_CHUNK 16            // tokens the scan fetches at a time
+#define M2_CHUNK 32            // tokens the scan fetches at a time
 #define M2_MAX_TAPS 16
 
 struct Segment { int first, count, before, slot; };
@@ -64,43 +64,63 @@ __global__ void __launch_bounds__(128) mamba2_conv_kernel(const T* u, int u_widt
     }
 }
 
-// grid (segments, heads); thread (part, e): value entry e = tid % P, state rows n = part, part + parts, ...
-template <typename T, int NPT>
-__global__ void __launch_bounds__(NPT <= 32 ? 1024 : 256) mamba2_scan_kernel(const T* u, int u_width, int dt_off, int conv_in_off, const float* c, int channels,
+// grid (segments, heads, slices of P): a CTA holds the columns [p0, p0 + P) of a head's state, P = Pf / slices (few
+// segments are cut into more slices, so that a prompt's recurrence runs on more SMs than the model has heads);
+// thread (part, e): value entry p0 + e, e = tid % P, state rows n = part, part + parts, ...
+template <typename T, int NPT, int MAXT>
+__global__ void __launch_bounds__(MAXT) mamba2_scan_kernel(const T* u, int u_width, int dt_off, int conv_in_off, const float* c, int channels,
                                    const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
                                    const Segment* __restrict__ segs, float* state, long long state_stride, long long conv_off,
-                                   float* __restrict__ y, int heads, int groups, int P, int N, int taps, int parts) {
+                                   float* __restrict__ y, int heads, int groups, int Pf, int P, int N, int taps, int parts) {
     extern __shared__ float smem[];
+    const int NP = NPT * parts;                      // rows of B and C in shared memory: N, padded with zeros to what the threads hold
     float* x_s = smem;                              // [M2_CHUNK][P]
-    float* b_s = x_s + M2_CHUNK * P;                // [M2_CHUNK][N]
-    float* c_s = b_s + M2_CHUNK * N;                // [M2_CHUNK][N]
-    float* dt_s = c_s + M2_CHUNK * N;               // [M2_CHUNK] dt, then [M2_CHUNK] decay
+    float* b_s = x_s + M2_CHUNK * P;                // [M2_CHUNK][NP]
+    float* c_s = b_s + M2_CHUNK * NP;               // [M2_CHUNK][NP]
+    float* dt_s = c_s + M2_CHUNK * NP;              // [M2_CHUNK] dt, then [M2_CHUNK] decay
     float* y_s = dt_s + 2 * M2_CHUNK;               // [M2_CHUNK][parts][P]
     pdl_launch_dependents();
     pdl_wait(KID_MAMBA2);
     const Segment s = segs[blockIdx.x];
     if (s.count <= 0) return;
-    const int h = blockIdx.y, g = h / (heads / groups);
-    const int inner = heads * P;
+    const int h = blockIdx.y, g = h / (heads / groups), p0 = blockIdx.z * P;
+    const int inner = heads * Pf;
     const int e = threadIdx.x % P, part = threadIdx.x / P;
     const bool worker = part < parts;
-    float* S = state + (size_t)s.slot * state_stride + (size_t)h * N * P;
+    float* S = state + (size_t)s.slot * state_stride + (size_t)h * N * Pf + p0;
     float st[NPT];
 #pragma unroll
     for (int k = 0; k < NPT; k++) {
         const int n = part + k * parts;
-        st[k] = (worker && n < N && s.before > 0) ? S[(size_t)n * P + e] : 0.f;
+        st[k] = (worker && n < N && s.before > 0) ? S[(size_t)n * Pf + e] : 0.f;
     }
     const float A = -expf(a_log[h]), Dh = d_skip[h], bias = dt_bias[h];
+    const bool vec4 = P % 4 == 0 && N % 4 == 0 && Pf % 4 == 0 && channels % 4 == 0 && NP % 4 == 0;
+    for (int i = threadIdx.x; i < 2 * M2_CHUNK * NP; i += blockDim.x) b_s[i] = 0.f;      // (the padding rows stay zero)
     for (int t0 = 0; t0 < s.count; t0 += M2_CHUNK) {
         const int nt = min(M2_CHUNK, s.count - t0);
         __syncthreads();
-        for (int i = threadIdx.x; i < nt * P; i += blockDim.x)
-            x_s[i] = c[(size_t)(s.first + t0 + i / P) * channels + h * P + i % P];
-        for (int i = threadIdx.x; i < nt * N; i += blockDim.x) {
-            const size_t row = (size_t)(s.first + t0 + i / N) * channels;
-            b_s[i] = c[row + inner + g * N + i % N];
-            c_s[i] = c[row + inner + groups * N + g * N + i % N];
+        if (vec4) {
+            // rows of whole float4s on 16-byte boundaries: four values a load, a thread's loads in flight together
+            const int pv = P / 4, nv = N / 4;
+            for (int i = threadIdx.x; i < nt * pv; i += blockDim.x)
+                *reinterpret_cast<float4*>(x_s + (i / pv) * P + (i % pv) * 4) =
+                    *reinterpret_cast<const float4*>(c + (size_t)(s.first + t0 + i / pv) * channels + h * Pf + p0 + (i % pv) * 4);
+#pragma unroll 4
+            for (int i = threadIdx.x; i < nt * nv; i += blockDim.x) {
+                const float* row = c + (size_t)(s.first + t0 + i / nv) * channels + inner + g * N + (i % nv) * 4;
+                const float4 bv = *reinterpret_cast<const float4*>(row), cv = *reinterpret_cast<const float4*>(row + groups * N);
+                *reinterpret_cast<float4*>(b_s + (i / nv) * NP + (i % nv) * 4) = bv;
+                *reinterpret_cast<float4*>(c_s + (i / nv) * NP + (i % nv) * 4) = cv;
+            }
+        } else {
+            for (int i = threadIdx.x; i < nt * P; i += blockDim.x)
+                x_s[i] = c[(size_t)(s.first + t0 + i / P) * channels + h * Pf + p0 + i % P];
+            for (int i = threadIdx.x; i < nt * N; i += blockDim.x) {
+                const size_t row = (size_t)(s.first + t0 + i / N) * channels;
+                b_s[(i / N) * NP + i % N] = c[row + inner + g * N + i % N];
+                c_s[(i / N) * NP + i % N] = c[row + inner + groups * N + g * N + i % N];
+            }
         }
         if (threadIdx.x < nt) {
             const float dt = softplus_f(to_f32(u[(size_t)(s.first + t0 + threadIdx.x) * u_width + dt_off + h]) + bias);
@@ -109,21 +129,24 @@ __global__ void __launch_bounds__(NPT <= 32 ? 1024 : 256) mamba2_scan_kernel(con
         }
         __syncthreads();
         if (worker) {
+            // (rows past N hold zeros in b_s and c_s: their state stays zero and adds nothing, so no row is tested here;
+            //  a token's B and C come into registers in one go, ahead of the products that need them)
+#pragma unroll 2
             for (int t = 0; t < nt; t++) {
                 const float dt = dt_s[t], a = dt_s[M2_CHUNK + t];
                 const float dx = dt * x_s[t * P + e];
-                const float* bt = b_s + t * N;
-                const float* ct = c_s + t * N;
-                float acc = 0.f;
+                const float* bt = b_s + t * NP + part;
+                const float* ct = c_s + t * NP + part;
+                float bv[NPT], cv[NPT];
+#pragma unroll
+                for (int k = 0; k < NPT; k++) { bv[k] = bt[k * parts]; cv[k] = ct[k * parts]; }
+                float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
                 for (int k = 0; k < NPT; k++) {
-                    const int n = part + k * parts;
-                    if (n < N) {
-                        st[k] = fmaf(a, st[k], dx * bt[n]);
-                        acc = fmaf(st[k], ct[n], acc);
-                    }
+                    st[k] = fmaf(a, st[k], dx * bv[k]);
+                    if (k & 1) acc1 = fmaf(st[k], cv[k], acc1); else acc0 = fmaf(st[k], cv[k], acc0);
                 }
-                y_s[(t * parts + part) * P + e] = acc;
+                y_s[(t * parts + part) * P + e] = acc0 + acc1;
             }
         }
         __syncthreads();
@@ -131,24 +154,24 @@ __global__ void __launch_bounds__(NPT <= 32 ? 1024 : 256) mamba2_scan_kernel(con
             const int t = i / P, ee = i % P;
             float acc = 0.f;
             for (int q = 0; q < parts; q++) acc += y_s[(t * parts + q) * P + ee];     // always in the order of the parts
-            y[(size_t)(s.first + t0 + t) * inner + h * P + ee] = acc + Dh * x_s[t * P + ee];
+            y[(size_t)(s.first + t0 + t) * inner + h * Pf + p0 + ee] = acc + Dh * x_s[t * P + ee];
         }
     }
     if (worker) {
 #pragma unroll
         for (int k = 0; k < NPT; k++) {
             const int n = part + k * parts;
-            if (n < N) S[(size_t)n * P + e] = st[k];
+            if (n < N) S[(size_t)n * Pf + e] = st[k];
         }
     }
     // The convolution's state: the last taps - 1 inputs of this head's channels (x), and of its group's B and C by the
     // group's first head.  The convolution kernel has finished; nobody else touches these channels.
     float* cs = state + (size_t)s.slot * state_stride + conv_off;
     const int hpg = heads / groups;
-    const int extra = (h % hpg == 0) ? 2 * N : 0;
+    const int extra = (h % hpg == 0 && blockIdx.z == 0) ? 2 * N : 0;
     for (int i = threadIdx.x; i < P + extra; i += blockDim.x) {
         int ch;
-        if (i < P) ch = h * P + i;
+        if (i < P) ch = h * Pf + p0 + i;
         else if (i < P + N) ch = inner + g * N + (i - P);
         else ch = inner + groups * N + g * N + (i - P - N);
         float keep[M2_MAX_TAPS];
@@ -194,14 +217,18 @@ __global__ void __launch_bounds__(256) mamba2_gate_norm_kernel(const float* y, c
     }
 }
 
-template <typename T, int NPT>
-static void launch_scan(int threads, size_t smem, dim3 grid, cudaStream_t stream, const void* u, int u_width, int dt_off, int conv_in_off,
-                        const float* c, int channels, const float* dt_bias, const float* a_log, const float* d_skip, const int* segs,
-                        float* state, long long state_stride, long long conv_off, float* y, int heads, int groups, int P, int N, int taps,
-                        int parts) {
-    cudaFuncSetAttribute(mamba2_scan_kernel<T, NPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    launch_chained(mamba2_scan_kernel<T, NPT>, grid, dim3(threads), smem, stream, (const T*)u, u_width, dt_off, conv_in_off, c, channels,
-                   dt_bias, a_log, d_skip, (const Segment*)segs, state, state_stride, conv_off, y, heads, groups, P, N, taps, parts);
+struct ScanArgs {
+    int threads; size_t smem; dim3 grid; cudaStream_t stream; const void* u; int u_width, dt_off, conv_in_off; const float* c; int channels;
+    const float *dt_bias, *a_log, *d_skip; const int* segs; float* state; long long state_stride, conv_off; float* y;
+    int heads, groups, Pf, P, N, taps, parts;
+};
+
+template <typename T, int NPT, int MAXT>
+static void launch_scan(const ScanArgs& a) {
+    cudaFuncSetAttribute(mamba2_scan_kernel<T, NPT, MAXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)a.smem);
+    launch_chained(mamba2_scan_kernel<T, NPT, MAXT>, a.grid, dim3(a.threads), a.smem, a.stream, (const T*)a.u, a.u_width, a.dt_off,
+                   a.conv_in_off, a.c, a.channels, a.dt_bias, a.a_log, a.d_skip, (const Segment*)a.segs, a.state, a.state_stride,
+                   a.conv_off, a.y, a.heads, a.groups, a.Pf, a.P, a.N, a.taps, a.parts);
 }
 
 // u: [tokens, 2 inner + 2 G N + heads] of the compute dtype; conv_w [channels, taps], conv_b [channels] of the same;
@@ -220,30 +247,40 @@ PLLM_EXPORT int pllm_mamba2_mix(int dtype, const void* u, const void* conv_w, co
     const int u_width = 2 * inner + 2 * groups * N + heads;
     const long long conv_off = (long long)heads * N * P;
     if (state_stride < conv_off + (long long)(taps - 1) * channels) return PLLM_ERR_SIZE;
-    // threads of the scan: as many parts of P threads as fit 256 (1024 where a thread would hold more than 64 state rows;
+    // Slices of P: a step of few segments (a prompt's portion) is cut so that segments x heads x slices fills the SMs,
+    // slices of at least 16 columns that divide P.
+    int slices = 1;
+    while (slices < 8 && (long long)n_segs * heads * slices < sm_count() && P % (2 * slices) == 0 && P / (2 * slices) >= 16) slices *= 2;
+    const int Ps = P / slices;
+    // threads of the scan: as many parts of Ps threads as fit 256 (1024 where a thread would hold more than 64 state rows;
     // a thread of 1024 holds 32 at most, for the registers to suffice)
     int threads = 256;
-    if (P > 256 || (N + (256 / P) - 1) / (256 / P) > 64) threads = 1024;
-    int parts = threads / P;
+    if (Ps > 256 || (N + (256 / Ps) - 1) / (256 / Ps) > 64) threads = 1024;
+    const bool big = threads == 1024;
+    int parts = threads / Ps;
     if (parts > N) parts = N;
     const int npt = (N + parts - 1) / parts;
-    if (npt > (threads == 1024 ? 32 : 64)) return PLLM_ERR_LIMIT;
-    threads = (parts * P + 31) / 32 * 32;
-    if (threads < M2_CHUNK) threads = 32;
-    const size_t smem = ((size_t)M2_CHUNK * P + 2 * (size_t)M2_CHUNK * N + 2 * M2_CHUNK + (size_t)M2_CHUNK * parts * P) * sizeof(float);
+    if (npt > (big ? 32 : 64)) return PLLM_ERR_LIMIT;
+    threads = (parts * Ps + 31) / 32 * 32;
+    if (threads < M2_CHUNK) threads = M2_CHUNK;
+    // (state rows a thread as the kernels are instantiated: the rows of B and C in shared memory are padded to that)
+    const int npt_t = big ? (npt <= 8 ? 8 : npt <= 16 ? 16 : 32) : (npt <= 4 ? 4 : npt <= 8 ? 8 : npt <= 16 ? 16 : npt <= 32 ? 32 : 64);
+    const size_t smem = ((size_t)M2_CHUNK * Ps + 2 * (size_t)M2_CHUNK * npt_t * parts + 2 * M2_CHUNK + (size_t)M2_CHUNK * parts * Ps) * sizeof(float);
     if (smem > 200 * 1024) return PLLM_ERR_LIMIT;
     const int chunks = (max_segment_tokens + M2_CONV_TOKENS - 1) / M2_CONV_TOKENS;
     PLLM_DISPATCH_DTYPE(dtype, {
         launch_chained(mamba2_conv_kernel<T>, dim3(n_segs, (channels + 127) / 128, chunks > 0 ? chunks : 1), dim3(128), 0, stream,
                        (const T*)u, u_width, inner, (const T*)conv_w, (const T*)conv_b, (const Segment*)segs, (const float*)state,
                        state_stride, conv_off, c_buf, channels, taps);
-        const dim3 grid(n_segs, heads);
-        const int dt_off = 2 * inner + 2 * groups * N;
-        if (npt <= 4) launch_scan<T, 4>(threads, smem, grid, stream, u, u_width, dt_off, inner, c_buf, channels, dt_bias, a_log, d_skip, segs, state, state_stride, conv_off, y_buf, heads, groups, P, N, taps, parts);
-        else if (npt <= 8) launch_scan<T, 8>(threads, smem, grid, stream, u, u_width, dt_off, inner, c_buf, channels, dt_bias, a_log, d_skip, segs, state, state_stride, conv_off, y_buf, heads, groups, P, N, taps, parts);
-        else if (npt <= 16) launch_scan<T, 16>(threads, smem, grid, stream, u, u_width, dt_off, inner, c_buf, channels, dt_bias, a_log, d_skip, segs, state, state_stride, conv_off, y_buf, heads, groups, P, N, taps, parts);
-        else if (npt <= 32) launch_scan<T, 32>(threads, smem, grid, stream, u, u_width, dt_off, inner, c_buf, channels, dt_bias, a_log, d_skip, segs, state, state_stride, conv_off, y_buf, heads, groups, P, N, taps, parts);
-        else launch_scan<T, 64>(threads, smem, grid, stream, u, u_width, dt_off, inner, c_buf, channels, dt_bias, a_log, d_skip, segs, state, state_stride, conv_off, y_buf, heads, groups, P, N, taps, parts);
+        ScanArgs a{threads, smem, dim3(n_segs, heads, slices), stream, u, u_width, 2 * inner + 2 * groups * N, inner, c_buf, channels, dt_bias,
+                   a_log, d_skip, segs, state, state_stride, conv_off, y_buf, heads, groups, P, Ps, N, taps, parts};
+        if (big) {
+            if (npt_t == 8) launch_scan<T, 8, 1024>(a); else if (npt_t == 16) launch_scan<T, 16, 1024>(a); else launch_scan<T, 32, 1024>(a);
+        } else if (npt_t == 4) launch_scan<T, 4, 256>(a);
+        else if (npt_t == 8) launch_scan<T, 8, 256>(a);
+        else if (npt_t == 16) launch_scan<T, 16, 256>(a);
+        else if (npt_t == 32) launch_scan<T, 32, 256>(a);
+        else launch_scan<T, 64, 256>(a);
         launch_chained(mamba2_gate_norm_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, (const float*)y_buf, (const T*)u, u_width, gain,
                        (T*)out, inner, norm_groups, eps);
     });
