@@ -289,7 +289,9 @@ PLLM_EXPORT int pllm_attention_sink(int dtype, const void* q, const void* kv_poo
 // (cp.async, 16 bytes a thread; rows past the range or in pages given back are zero-filled) into padded rows of shared
 // memory; S = Q K^T and O += P V are mma.sync m16n8k16 products with float accumulators, the operands fetched with
 // ldmatrix (V transposed on the way); scale, cap, mask and the running softmax act on the accumulator registers.  A warp
-// skips tiles none of its rows can see.  Key and value sizes are template parameters (32, 64 or 128 each).
+// skips tiles none of its rows can see.  An item of 16 rows or fewer (decoded tokens) is shared out the other way: every
+// warp holds the same rows and takes 16 keys of each tile, and the four partial results meet in shared memory at the end.
+// Key and value sizes are template parameters (32, 64 or 128 each).
 #define SMMA_BK 64
 #define SMMA_ROWS 64
 #define SMMA_PAD 8
@@ -331,9 +333,8 @@ __global__ void __launch_bounds__(128) attention_sink_mma_kernel(const bf16* q, 
     constexpr int QS = DK + SMMA_PAD, KS = DK + SMMA_PAD, VS = DV + SMMA_PAD;      // row strides in elements
     extern __shared__ __align__(16) unsigned char sink_smem[];
     bf16* q_s = reinterpret_cast<bf16*>(sink_smem);            // [SMMA_ROWS][QS]
-    bf16* k_s = q_s + SMMA_ROWS * QS;                          // [SMMA_BK][KS]
-    bf16* v_s = k_s + SMMA_BK * KS;                            // [SMMA_BK][VS]
-    __shared__ int page_s[SMMA_BK];
+    bf16* k_s = q_s + SMMA_ROWS * QS;                          // the tiles' place
+    constexpr int TILE = SMMA_BK * (KS + VS);                  // a tile's keys [SMMA_BK][KS], then its values [SMMA_BK][VS]; two tiles
     pdl_launch_dependents();
     pdl_wait(KID_ATT_SINK);
     if ((int)blockIdx.x >= *n_work_ptr) return;
@@ -357,17 +358,19 @@ __global__ void __launch_bounds__(128) attention_sink_mma_kernel(const bf16* q, 
         *reinterpret_cast<uint4*>(q_s + r * QS + c) = v;
     }
     __syncthreads();
+    const bool ksplit = rows <= 16;                  // the warps share the keys of a tile, not the rows
+    const int row_base = ksplit ? 0 : warp * 16;
     uint32_t qf[DK / 16][4];
 #pragma unroll
     for (int kk = 0; kk < DK / 16; kk++)
-        sink_ldmatrix_x4(qf[kk], sink_smem_u32(q_s + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * QS + kk * 16 + (lane >> 4) * 8));
+        sink_ldmatrix_x4(qf[kk], sink_smem_u32(q_s + (row_base + (lane & 7) + ((lane >> 3) & 1) * 8) * QS + kk * 16 + (lane >> 4) * 8));
 
-    // this thread's two rows: r0 = warp * 16 + g and r0 + 8
-    const int r0 = warp * 16 + g, r1 = r0 + 8;
+    // this thread's two rows: r0 = row_base + g and r0 + 8
+    const int r0 = row_base + g, r1 = r0 + 8;
     const int pos0 = w.q_pos0 + (r0 < rows ? r0 / n_heads : 0), pos1 = w.q_pos0 + (r1 < rows ? r1 / n_heads : 0);
     const bool live0 = r0 < rows, live1 = r1 < rows;
     // positions of the warp's rows, for skipping tiles: rows warp*16 .. warp*16+15 that exist
-    const int wr_lo = warp * 16, wr_hi = min(rows, warp * 16 + 16) - 1;
+    const int wr_lo = row_base, wr_hi = min(rows, row_base + 16) - 1;
     const bool warp_live = wr_lo < rows;
     const int wpos_lo = w.q_pos0 + wr_lo / n_heads, wpos_hi = w.q_pos0 + (warp_live ? wr_hi / n_heads : 0);
 
@@ -377,106 +380,169 @@ __global__ void __launch_bounds__(128) attention_sink_mma_kernel(const bf16* q, 
     for (int j = 0; j < DV / 8; j++) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
     const int* table = block_tables + (size_t)w.seg * table_width;
 
-    for (int range = 0; range < 2; range++) {
-        const int r_begin = range == 0 ? 0 : w.kv_begin;
-        const int r_end = range == 0 ? (first_split && window > 0 ? min(keep_first, w.kv_begin) : 0) : w.kv_end;
-        for (int kv0 = r_begin; kv0 < r_end; kv0 += SMMA_BK) {
-            __syncthreads();                 // the tile before is no longer read
-            if (threadIdx.x < SMMA_BK) {
-                const int j = kv0 + threadIdx.x;
-                int page = -1;
-                if (j < r_end) {
-                    const int b = j / page_size;
-                    page = b < table_width ? table[b] : -1;
-                    if (page >= n_pages) { atomicOr(status, 8); page = -1; }
+    // The tiles of the item, in order: those of the kept first tokens before its range (first split only), then its range.
+    const int r0_end = first_split && window > 0 ? min(keep_first, w.kv_begin) : 0;
+    const int n0 = (r0_end + SMMA_BK - 1) / SMMA_BK, n_tiles = n0 + (max(w.kv_end - w.kv_begin, 0) + SMMA_BK - 1) / SMMA_BK;
+    // Tile i + 1 is on its way (cp.async into the other half of the tiles' place) while tile i is multiplied; a row's
+    // page is looked up by the thread that copies it, a tile ahead, so no lookup stands between a tile and its copy.
+    auto issue = [&](int i) {
+        const int kv0 = i < n0 ? i * SMMA_BK : w.kv_begin + (i - n0) * SMMA_BK, r_end = i < n0 ? r0_end : w.kv_end;
+        bf16* kb = k_s + (i & 1) * TILE, * vb = kb + SMMA_BK * KS;
+        // four threads a row: the row's page is looked up once, then each copies every fourth 16-byte piece of it
+        constexpr int CPR = WROW / 8;
+#pragma unroll
+        for (int pass = 0; pass < SMMA_BK / 32; pass++) {
+            const int j = pass * 32 + (threadIdx.x >> 2), q4 = threadIdx.x & 3;
+            int page = -1;
+            if (kv0 + j < r_end) {
+                const int b = (kv0 + j) / page_size;
+                page = b < table_width ? __ldg(table + b) : -1;
+                if (page >= n_pages) { atomicOr(status, 8); page = -1; }
+            }
+            const bf16* src = kv_pool + (((size_t)max(page, 0) * nkv + kh) * page_size + (kv0 + j) % page_size) * WROW;
+            bf16* kd = kb + j * KS;
+            bf16* vd = vb + j * VS - DK;
+#pragma unroll
+            for (int k = 0; k < CPR / 4; k++) {
+                const int c = (q4 + 4 * k) * 8;
+                sink_cp_async16(sink_smem_u32(c < DK ? kd + c : vd + c), src + c, page >= 0);
+            }
+        }
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+    if (n_tiles > 0) issue(0);
+    for (int i = 0; i < n_tiles; i++) {
+        const int kv0 = i < n0 ? i * SMMA_BK : w.kv_begin + (i - n0) * SMMA_BK, r_end = i < n0 ? r0_end : w.kv_end;
+        const bf16* k_t = k_s + (i & 1) * TILE;
+        const bf16* v_t = k_t + SMMA_BK * KS;
+        if (i + 1 < n_tiles) {
+            issue(i + 1);
+            asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        }
+        __syncthreads();                     // tile i has landed for every thread
+        {
+            // can any row of this warp see any key of (its share of) the tile?
+            const int t_lo = ksplit ? kv0 + warp * 16 : kv0;
+            const int t_hi = min(ksplit ? t_lo + 16 : kv0 + SMMA_BK, r_end) - 1;
+            bool any = warp_live && t_lo <= wpos_hi && t_lo < r_end;
+            if (any && window > 0) any = t_hi > wpos_lo - window || t_lo < keep_first;
+            if (any) {
+                float sc[SMMA_BK / 8][4];
+#pragma unroll
+                for (int j = 0; j < SMMA_BK / 8; j++) { sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f; }
+#pragma unroll
+                for (int kk = 0; kk < DK / 16; kk++) {
+#pragma unroll
+                    for (int j = 0; j < SMMA_BK / 8; j += 2) {
+                        if (ksplit && j != 2 * warp) continue;
+                        uint32_t b[4];
+                        sink_ldmatrix_x4(b, sink_smem_u32(k_t + (j * 8 + (lane & 7) + (lane >> 4) * 8) * KS + kk * 16 + ((lane >> 3) & 1) * 8));
+                        sink_mma_bf16(sc[j], qf[kk], b[0], b[1]);
+                        sink_mma_bf16(sc[j + 1], qf[kk], b[2], b[3]);
+                    }
                 }
-                page_s[threadIdx.x] = page;
-            }
-            __syncthreads();
-            for (int idx = threadIdx.x; idx < SMMA_BK * (WROW / 8); idx += blockDim.x) {
-                const int j = idx / (WROW / 8), c = (idx % (WROW / 8)) * 8;
-                const int page = page_s[j];
-                const bf16* src = kv_pool + (((size_t)max(page, 0) * nkv + kh) * page_size + (kv0 + j) % page_size) * WROW + c;
-                bf16* dst = c < DK ? k_s + j * KS + c : v_s + j * VS + (c - DK);
-                sink_cp_async16(sink_smem_u32(dst), src, page >= 0);
-            }
-            sink_cp_async_wait_all();
-            __syncthreads();
-            // can any row of this warp see any key of the tile?
-            const int t_hi = min(kv0 + SMMA_BK, r_end) - 1;
-            bool any = warp_live && kv0 <= wpos_hi;
-            if (any && window > 0) any = t_hi > wpos_lo - window || kv0 < keep_first;
-            if (!any) continue;
-
-            float sc[SMMA_BK / 8][4];
+                // scale, cap, mask; the tile's row maxima
+                float tm0 = -CUDART_INF_F, tm1 = -CUDART_INF_F;
 #pragma unroll
-            for (int j = 0; j < SMMA_BK / 8; j++) { sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f; }
+                for (int j = 0; j < SMMA_BK / 8; j++) {
+                    if (ksplit && (j >> 1) != warp) continue;          // (another warp's keys: left out of everything below)
 #pragma unroll
-            for (int kk = 0; kk < DK / 16; kk++) {
-#pragma unroll
-                for (int j = 0; j < SMMA_BK / 8; j += 2) {
-                    uint32_t b[4];
-                    sink_ldmatrix_x4(b, sink_smem_u32(k_s + (j * 8 + (lane & 7) + (lane >> 4) * 8) * KS + kk * 16 + ((lane >> 3) & 1) * 8));
-                    sink_mma_bf16(sc[j], qf[kk], b[0], b[1]);
-                    sink_mma_bf16(sc[j + 1], qf[kk], b[2], b[3]);
+                    for (int e = 0; e < 4; e++) {
+                        const int key = kv0 + j * 8 + t4 * 2 + (e & 1);
+                        const int pos = e < 2 ? pos0 : pos1;
+                        const bool live = e < 2 ? live0 : live1;
+                        const bool seen = live && key < r_end && key <= pos && (window <= 0 || pos - key < window || key < keep_first);
+                        float v = sc[j][e] * scale;
+                        // tanh(x) = 1 - 2 / (exp(2x) + 1) with the fast exponential and division: its absolute error (1e-7) is far
+                        // below what the bfloat16 operands leave in the score
+                        if (cap > 0.f) v = cap * (1.0f - __fdividef(2.0f, __expf(2.0f * v * inv_cap) + 1.0f));
+                        v = seen ? v : -CUDART_INF_F;
+                        sc[j][e] = v;
+                        if (e < 2) tm0 = fmaxf(tm0, v); else tm1 = fmaxf(tm1, v);
+                    }
                 }
-            }
-            // scale, cap, mask; the tile's row maxima
-            float tm0 = -CUDART_INF_F, tm1 = -CUDART_INF_F;
+                tm0 = fmaxf(tm0, __shfl_xor_sync(0xffffffffu, tm0, 1)); tm0 = fmaxf(tm0, __shfl_xor_sync(0xffffffffu, tm0, 2));
+                tm1 = fmaxf(tm1, __shfl_xor_sync(0xffffffffu, tm1, 1)); tm1 = fmaxf(tm1, __shfl_xor_sync(0xffffffffu, tm1, 2));
+                const float mn0 = fmaxf(m0, tm0), mn1 = fmaxf(m1, tm1);
+                const float c0 = mn0 == -CUDART_INF_F ? 1.f : __expf(m0 - mn0), c1 = mn1 == -CUDART_INF_F ? 1.f : __expf(m1 - mn1);
+                float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-            for (int j = 0; j < SMMA_BK / 8; j++) {
-#pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    const int key = kv0 + j * 8 + t4 * 2 + (e & 1);
-                    const int pos = e < 2 ? pos0 : pos1;
-                    const bool live = e < 2 ? live0 : live1;
-                    const bool seen = live && key < r_end && key <= pos && (window <= 0 || pos - key < window || key < keep_first);
-                    float v = sc[j][e] * scale;
-                    // tanh(x) = 1 - 2 / (exp(2x) + 1) with the fast exponential and division: its absolute error (1e-7) is far
-                    // below what the bfloat16 operands leave in the score
-                    if (cap > 0.f) v = cap * (1.0f - __fdividef(2.0f, __expf(2.0f * v * inv_cap) + 1.0f));
-                    v = seen ? v : -CUDART_INF_F;
-                    sc[j][e] = v;
-                    if (e < 2) tm0 = fmaxf(tm0, v); else tm1 = fmaxf(tm1, v);
+                for (int j = 0; j < SMMA_BK / 8; j++) {
+                    if (ksplit && (j >> 1) != warp) continue;
+                    sc[j][0] = mn0 == -CUDART_INF_F ? 0.f : __expf(sc[j][0] - mn0);
+                    sc[j][1] = mn0 == -CUDART_INF_F ? 0.f : __expf(sc[j][1] - mn0);
+                    sc[j][2] = mn1 == -CUDART_INF_F ? 0.f : __expf(sc[j][2] - mn1);
+                    sc[j][3] = mn1 == -CUDART_INF_F ? 0.f : __expf(sc[j][3] - mn1);
+                    s0 += sc[j][0] + sc[j][1];
+                    s1 += sc[j][2] + sc[j][3];
                 }
-            }
-            tm0 = fmaxf(tm0, __shfl_xor_sync(0xffffffffu, tm0, 1)); tm0 = fmaxf(tm0, __shfl_xor_sync(0xffffffffu, tm0, 2));
-            tm1 = fmaxf(tm1, __shfl_xor_sync(0xffffffffu, tm1, 1)); tm1 = fmaxf(tm1, __shfl_xor_sync(0xffffffffu, tm1, 2));
-            const float mn0 = fmaxf(m0, tm0), mn1 = fmaxf(m1, tm1);
-            const float c0 = mn0 == -CUDART_INF_F ? 1.f : __expf(m0 - mn0), c1 = mn1 == -CUDART_INF_F ? 1.f : __expf(m1 - mn1);
-            float s0 = 0.f, s1 = 0.f;
+                s0 += __shfl_xor_sync(0xffffffffu, s0, 1); s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
+                s1 += __shfl_xor_sync(0xffffffffu, s1, 1); s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+                l0 = l0 * c0 + s0; l1 = l1 * c1 + s1;
+                m0 = mn0; m1 = mn1;
 #pragma unroll
-            for (int j = 0; j < SMMA_BK / 8; j++) {
-                sc[j][0] = mn0 == -CUDART_INF_F ? 0.f : __expf(sc[j][0] - mn0);
-                sc[j][1] = mn0 == -CUDART_INF_F ? 0.f : __expf(sc[j][1] - mn0);
-                sc[j][2] = mn1 == -CUDART_INF_F ? 0.f : __expf(sc[j][2] - mn1);
-                sc[j][3] = mn1 == -CUDART_INF_F ? 0.f : __expf(sc[j][3] - mn1);
-                s0 += sc[j][0] + sc[j][1];
-                s1 += sc[j][2] + sc[j][3];
-            }
-            s0 += __shfl_xor_sync(0xffffffffu, s0, 1); s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
-            s1 += __shfl_xor_sync(0xffffffffu, s1, 1); s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
-            l0 = l0 * c0 + s0; l1 = l1 * c1 + s1;
-            m0 = mn0; m1 = mn1;
+                for (int j = 0; j < DV / 8; j++) { o[j][0] *= c0; o[j][1] *= c0; o[j][2] *= c1; o[j][3] *= c1; }
+                // O += P V
 #pragma unroll
-            for (int j = 0; j < DV / 8; j++) { o[j][0] *= c0; o[j][1] *= c0; o[j][2] *= c1; o[j][3] *= c1; }
-            // O += P V
+                for (int kk = 0; kk < SMMA_BK / 16; kk++) {
+                    if (ksplit && kk != warp) continue;
+                    uint32_t a[4];
+                    a[0] = sink_pack_bf16(sc[2 * kk][0], sc[2 * kk][1]);
+                    a[1] = sink_pack_bf16(sc[2 * kk][2], sc[2 * kk][3]);
+                    a[2] = sink_pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
+                    a[3] = sink_pack_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
 #pragma unroll
-            for (int kk = 0; kk < SMMA_BK / 16; kk++) {
-                uint32_t a[4];
-                a[0] = sink_pack_bf16(sc[2 * kk][0], sc[2 * kk][1]);
-                a[1] = sink_pack_bf16(sc[2 * kk][2], sc[2 * kk][3]);
-                a[2] = sink_pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
-                a[3] = sink_pack_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
-#pragma unroll
-                for (int j = 0; j < DV / 8; j += 2) {
-                    uint32_t b[4];
-                    sink_ldmatrix_x4_trans(b, sink_smem_u32(v_s + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VS + j * 8 + (lane >> 4) * 8));
-                    sink_mma_bf16(o[j], a, b[0], b[1]);
-                    sink_mma_bf16(o[j + 1], a, b[2], b[3]);
+                    for (int j = 0; j < DV / 8; j += 2) {
+                        uint32_t b[4];
+                        sink_ldmatrix_x4_trans(b, sink_smem_u32(v_t + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VS + j * 8 + (lane >> 4) * 8));
+                        sink_mma_bf16(o[j], a, b[0], b[1]);
+                        sink_mma_bf16(o[j + 1], a, b[2], b[3]);
+                    }
                 }
             }
         }
+        __syncthreads();                     // before the copy of tile i + 2 overwrites this half
+    }
+    if (ksplit) {
+        // the four warps' partial results of the same rows meet: (max, sum, output) a warp and row
+        float* comb = reinterpret_cast<float*>(k_s);          // [4 warps][16 rows][DV + 2]
+        __syncthreads();                                       // the last tile is no longer read
+        {
+            float* c0 = comb + ((size_t)warp * 16 + g) * (DV + 2);
+            float* c1 = c0 + 8 * (DV + 2);
+            if (t4 == 0) { c0[0] = m0; c0[1] = l0; c1[0] = m1; c1[1] = l1; }
+#pragma unroll
+            for (int j = 0; j < DV / 8; j++) {
+                c0[2 + j * 8 + t4 * 2] = o[j][0]; c0[2 + j * 8 + t4 * 2 + 1] = o[j][1];
+                c1[2 + j * 8 + t4 * 2] = o[j][2]; c1[2 + j * 8 + t4 * 2 + 1] = o[j][3];
+            }
+        }
+        __syncthreads();
+        if (warp != 0) return;
+        float M0 = -CUDART_INF_F, M1 = -CUDART_INF_F;
+#pragma unroll
+        for (int wq = 0; wq < 4; wq++) {
+            M0 = fmaxf(M0, comb[((size_t)wq * 16 + g) * (DV + 2)]);
+            M1 = fmaxf(M1, comb[((size_t)wq * 16 + g + 8) * (DV + 2)]);
+        }
+        l0 = l1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < DV / 8; j++) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+#pragma unroll
+        for (int wq = 0; wq < 4; wq++) {                       // always in the order of the warps
+            const float* c0 = comb + ((size_t)wq * 16 + g) * (DV + 2);
+            const float* c1 = c0 + 8 * (DV + 2);
+            const float f0 = c0[0] == -CUDART_INF_F ? 0.f : __expf(c0[0] - M0), f1 = c1[0] == -CUDART_INF_F ? 0.f : __expf(c1[0] - M1);
+            l0 += c0[1] * f0; l1 += c1[1] * f1;
+#pragma unroll
+            for (int j = 0; j < DV / 8; j++) {
+                o[j][0] = fmaf(c0[2 + j * 8 + t4 * 2], f0, o[j][0]); o[j][1] = fmaf(c0[2 + j * 8 + t4 * 2 + 1], f0, o[j][1]);
+                o[j][2] = fmaf(c1[2 + j * 8 + t4 * 2], f1, o[j][2]); o[j][3] = fmaf(c1[2 + j * 8 + t4 * 2 + 1], f1, o[j][3]);
+            }
+        }
+        m0 = M0; m1 = M1;
     }
     // the sink, then the rows leave
 #pragma unroll
@@ -528,7 +594,10 @@ static int launch_sink_mma(const void* q, const void* kv_pool, const int* block_
     const int group = nh / nkv;
     const int heads_per_cta = group < SMMA_ROWS ? group : SMMA_ROWS;
     const int gparts = (group + heads_per_cta - 1) / heads_per_cta;
-    const size_t smem = ((size_t)SMMA_ROWS * (DK + SMMA_PAD) + (size_t)SMMA_BK * (DK + SMMA_PAD) + (size_t)SMMA_BK * (DV + SMMA_PAD)) * sizeof(bf16);
+    size_t tiles = 2 * ((size_t)SMMA_BK * (DK + SMMA_PAD) + (size_t)SMMA_BK * (DV + SMMA_PAD)) * sizeof(bf16);
+    const size_t meet = (size_t)4 * 16 * (DV + 2) * sizeof(float);      // where the warps of a decoded token's item combine (the tiles' place)
+    if (tiles < meet) tiles = meet;
+    const size_t smem = (size_t)SMMA_ROWS * (DK + SMMA_PAD) * sizeof(bf16) + tiles;
     cudaFuncSetAttribute(attention_sink_mma_kernel<DK, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_chained(attention_sink_mma_kernel<DK, DV>, dim3(max_work, nkv * gparts), dim3(128), smem, stream, (const bf16*)q,
                    (const bf16*)kv_pool, block_tables, (const SinkWork*)work, n_work_ptr, (bf16*)out, part_o, part_ml, sinks, nh, nkv,
