@@ -576,25 +576,25 @@ def latent_beside_dense(size, layers, pk, clocks, steps, warmup, prefill_only=Fa
 
 # ---- the windowed-attention / state-space / clamped-experts decoder (Bumisun) beside the grouped-query dense one ------
 # Sizes that resemble real layers: the widths of the 0.6B and of a 2B-class shape; attention of sixteen heads over eight
-# kv heads, keys of 128 and values of 64 entries, a window of 1024 tokens that keeps the first four, half of each head
+# kv heads, keys of 128 and values of 64 entries, a window of 1024 tokens that keeps the first eight, half of each head
 # rotated; Mamba-2 layers of width / 32 heads of 64 with a state of 128 rows; layers alternate a state-space mixer with
 # a dense gated feed-forward and an attention mixer with routed experts that together are as wide as the dense one.
 HYBRID_SIZES = {
-    "1024": dict(width=1024, heads=16, kv_heads=8, dim=128, vdim=64, window=1024, keep_first=4, rot=64, m_heads=32, m_vdim=64,
+    "1024": dict(width=1024, heads=16, kv_heads=8, dim=128, vdim=64, window=1024, keep_first=8, rot=64, m_heads=32, m_vdim=64,
                  m_state=128, m_groups=1, conv=4, ff=3072, experts=16, top=4, expert_ff=768, shared_ff=768),
-    "2048": dict(width=2048, heads=16, kv_heads=8, dim=128, vdim=64, window=1024, keep_first=4, rot=64, m_heads=64, m_vdim=64,
+    "2048": dict(width=2048, heads=16, kv_heads=8, dim=128, vdim=64, window=1024, keep_first=8, rot=64, m_heads=64, m_vdim=64,
                  m_state=128, m_groups=1, conv=4, ff=6144, experts=32, top=4, expert_ff=1536, shared_ff=1536),
 }
 
 
 def hybrid_config(z, layers):
-    att = dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["dim"], vdim=z["vdim"], scale=z["dim"] ** -0.5, softcap=30.0,
+    att = dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["dim"], vdim=z["vdim"], scale=z["dim"] ** -0.5, softcap=50.0,
                mask=dict(size=z["window"], keep_first=z["keep_first"]), rot=dict(dims=z["rot"], base=10000.0), v_mix=True)
     ssm = dict(heads=z["m_heads"], vdim=z["m_vdim"], state=z["m_state"], groups=z["m_groups"], conv=z["conv"], norm_groups=1)
     dense = dict(kind="dense", ff=z["ff"])
     moe = dict(kind="moe", expert=dict(ff=z["expert_ff"], limit=7.0), shared=dict(ff=z["shared_ff"], limit=7.0),
                router=dict(experts=z["experts"], top=z["top"]))
-    return dict(architecture="Bumisun", vocab=LATENT_VOCAB, width=z["width"], norm=dict(eps=1e-6), residual_mult=0.7, logit_scale=0.5,
+    return dict(architecture="Bumisun", vocab=LATENT_VOCAB, width=z["width"], norm=dict(eps=1e-6), residual_mult=0.5, logit_scale=1.0,
                 layers=[dict(type="mamba2", mixer=ssm, mlp=dense) if i % 2 == 0 else dict(type="attention", mixer=att, mlp=moe)
                         for i in range(layers)])
 
@@ -702,7 +702,7 @@ def hybrid_kernels(z, pk):
         keys = sum(min(p + i + 1, W) + min(keep, max(0, p + i + 1 - W)) for _, c, p in segs for i in range(c))
         q, o = torch.randn(n, nh * dk, device=dev).to(bf), torch.empty(n, nh * dv, dtype=bf, device=dev)
         w = plan(segs, ops.attention_sink_tile_tokens(nh, nkv, bf, dk, dv), ops.attention_sink_ctas_per_item(nh, nkv, bf, dk, dv), W)(nh, dv)
-        ms = timed(lambda: ops.attention_sink(q, pool, tables, w, o, sinks, nh, nkv, dk, dv, W, keep, dk ** -0.5, 30.0, status))
+        ms = timed(lambda: ops.attention_sink(q, pool, tables, w, o, sinks, nh, nkv, dk, dv, W, keep, dk ** -0.5, 50.0, status))
         seg_keys = sum(min(p + c, W + c) for _, c, p in segs)            # cache rows a segment's queries read, once
         note(f"attention_sink_{case}", ms, seg_keys * nkv * (dk + dv) * 2 + n * nh * (dk + dv) * 2, 2 * nh * (dk + dv) * keys)
         o2 = torch.empty(n, nh * dk, dtype=bf, device=dev)
@@ -729,7 +729,7 @@ def hybrid_kernels(z, pk):
     for case, n in (("decode_b64", B), ("prefill_2048", T)):
         x32, d = torch.randn(n, z["width"], device=dev), torch.randn(n, z["width"], device=dev).to(bf)
         g1, y = torch.ones(z["width"], device=dev), torch.empty(n, z["width"], dtype=bf, device=dev)
-        ms = timed(lambda: ops.add_scaled_norm32(x32, d, 0.7, g1, 1e-6, y))
+        ms = timed(lambda: ops.add_scaled_norm32(x32, d, 0.5, g1, 1e-6, y))
         note(f"add_scaled_norm32_{case}", ms, n * z["width"] * (4 + 4 + 2 + 2), 0)
         x16 = x32.to(bf)
         ms = timed(lambda: ops.rmsnorm(x16, g1, 1e-6, y, delta=d, residual_out=x16))

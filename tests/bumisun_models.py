@@ -35,7 +35,7 @@ def dense(ff):
     return dict(kind="dense", ff=ff)
 
 
-def moe(experts, top, ff, limit=1.5, shared=None, shared_limit=2.0):
+def moe(experts, top, ff, limit=1.25, shared=None, shared_limit=2.0):
     m = dict(kind="moe", router=dict(experts=experts, top=top), expert=dict(ff=ff, limit=limit))
     if shared:
         m["shared"] = dict(ff=shared, limit=shared_limit)
@@ -70,8 +70,8 @@ ODD = model(333, 90, [
 
 # W: more heads than one CTA's rows, vector-sized heads, a window longer than the prompts, a wide state
 WIDE = model(512, 128, [
-    layer(attention(20, 1, 32, 32, 500, 4, rot=16, v_mix=True), moe(12, 4, 64, shared=96)),
-    layer(mamba2(8, 32, 64, groups=4, norm_groups=2), moe(12, 4, 64, shared=96)),
+    layer(attention(20, 1, 32, 32, 500, 4, rot=16, v_mix=True), moe(10, 4, 72, shared=88)),
+    layer(mamba2(8, 32, 64, groups=4, norm_groups=2), moe(10, 4, 72, shared=88)),
     layer(attention(20, 1, 32, 32, 500, 4, rot=16, v_mix=True), dense(256))], mult=0.5)
 
 # only state-space layers, and only attention layers
