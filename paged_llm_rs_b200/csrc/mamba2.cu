@@ -22,7 +22,7 @@
 enum : int { KID_MAMBA2 = 80 };
 
 #define M2_CONV_TOKENS 64      // tokens a CTA of the convolution
-#define M2_CHUNK 32            // tokens the scan fetches at a time
+#define M2_CHUNK 32            // tokens the scan fetches at a time, at most (fewer where shared memory is short)
 #define M2_MAX_TAPS 16
 
 struct Segment { int first, count, before, slot; };
@@ -71,14 +71,14 @@ template <typename T, int NPT, int MAXT>
 __global__ void __launch_bounds__(MAXT) mamba2_scan_kernel(const T* u, int u_width, int dt_off, int conv_in_off, const float* c, int channels,
                                    const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
                                    const Segment* __restrict__ segs, float* state, long long state_stride, long long conv_off,
-                                   float* __restrict__ y, int heads, int groups, int Pf, int P, int N, int taps, int parts) {
+                                   float* __restrict__ y, int heads, int groups, int Pf, int P, int N, int taps, int parts, int chunk) {
     extern __shared__ float smem[];
     const int NP = NPT * parts;                      // rows of B and C in shared memory: N, padded with zeros to what the threads hold
-    float* x_s = smem;                              // [M2_CHUNK][P]
-    float* b_s = x_s + M2_CHUNK * P;                // [M2_CHUNK][NP]
-    float* c_s = b_s + M2_CHUNK * NP;               // [M2_CHUNK][NP]
-    float* dt_s = c_s + M2_CHUNK * NP;              // [M2_CHUNK] dt, then [M2_CHUNK] decay
-    float* y_s = dt_s + 2 * M2_CHUNK;               // [M2_CHUNK][parts][P]
+    float* x_s = smem;                              // [chunk][P]
+    float* b_s = x_s + chunk * P;                // [chunk][NP]
+    float* c_s = b_s + chunk * NP;               // [chunk][NP]
+    float* dt_s = c_s + chunk * NP;              // [chunk] dt, then [chunk] decay
+    float* y_s = dt_s + 2 * chunk;               // [chunk][parts][P]
     pdl_launch_dependents();
     pdl_wait(KID_MAMBA2);
     const Segment s = segs[blockIdx.x];
@@ -96,9 +96,9 @@ __global__ void __launch_bounds__(MAXT) mamba2_scan_kernel(const T* u, int u_wid
     }
     const float A = -expf(a_log[h]), Dh = d_skip[h], bias = dt_bias[h];
     const bool vec4 = P % 4 == 0 && N % 4 == 0 && Pf % 4 == 0 && channels % 4 == 0 && NP % 4 == 0;
-    for (int i = threadIdx.x; i < 2 * M2_CHUNK * NP; i += blockDim.x) b_s[i] = 0.f;      // (the padding rows stay zero)
-    for (int t0 = 0; t0 < s.count; t0 += M2_CHUNK) {
-        const int nt = min(M2_CHUNK, s.count - t0);
+    for (int i = threadIdx.x; i < 2 * chunk * NP; i += blockDim.x) b_s[i] = 0.f;      // (the padding rows stay zero)
+    for (int t0 = 0; t0 < s.count; t0 += chunk) {
+        const int nt = min(chunk, s.count - t0);
         __syncthreads();
         if (vec4) {
             // rows of whole float4s on 16-byte boundaries: four values a load, a thread's loads in flight together
@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(MAXT) mamba2_scan_kernel(const T* u, int u_wid
         if (threadIdx.x < nt) {
             const float dt = softplus_f(to_f32(u[(size_t)(s.first + t0 + threadIdx.x) * u_width + dt_off + h]) + bias);
             dt_s[threadIdx.x] = dt;
-            dt_s[M2_CHUNK + threadIdx.x] = expf(A * dt);
+            dt_s[chunk + threadIdx.x] = expf(A * dt);
         }
         __syncthreads();
         if (worker) {
@@ -133,7 +133,7 @@ __global__ void __launch_bounds__(MAXT) mamba2_scan_kernel(const T* u, int u_wid
             //  a token's B and C come into registers in one go, ahead of the products that need them)
 #pragma unroll 2
             for (int t = 0; t < nt; t++) {
-                const float dt = dt_s[t], a = dt_s[M2_CHUNK + t];
+                const float dt = dt_s[t], a = dt_s[chunk + t];
                 const float dx = dt * x_s[t * P + e];
                 const float* bt = b_s + t * NP + part;
                 const float* ct = c_s + t * NP + part;
@@ -220,7 +220,7 @@ __global__ void __launch_bounds__(256) mamba2_gate_norm_kernel(const float* y, c
 struct ScanArgs {
     int threads; size_t smem; dim3 grid; cudaStream_t stream; const void* u; int u_width, dt_off, conv_in_off; const float* c; int channels;
     const float *dt_bias, *a_log, *d_skip; const int* segs; float* state; long long state_stride, conv_off; float* y;
-    int heads, groups, Pf, P, N, taps, parts;
+    int heads, groups, Pf, P, N, taps, parts, chunk;
 };
 
 template <typename T, int NPT, int MAXT>
@@ -228,7 +228,7 @@ static void launch_scan(const ScanArgs& a) {
     cudaFuncSetAttribute(mamba2_scan_kernel<T, NPT, MAXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)a.smem);
     launch_chained(mamba2_scan_kernel<T, NPT, MAXT>, a.grid, dim3(a.threads), a.smem, a.stream, (const T*)a.u, a.u_width, a.dt_off,
                    a.conv_in_off, a.c, a.channels, a.dt_bias, a.a_log, a.d_skip, (const Segment*)a.segs, a.state, a.state_stride,
-                   a.conv_off, a.y, a.heads, a.groups, a.Pf, a.P, a.N, a.taps, a.parts);
+                   a.conv_off, a.y, a.heads, a.groups, a.Pf, a.P, a.N, a.taps, a.parts, a.chunk);
 }
 
 // u: [tokens, 2 inner + 2 G N + heads] of the compute dtype; conv_w [channels, taps], conv_b [channels] of the same;
@@ -265,7 +265,10 @@ PLLM_EXPORT int pllm_mamba2_mix(int dtype, const void* u, const void* conv_w, co
     if (threads < M2_CHUNK) threads = M2_CHUNK;
     // (state rows a thread as the kernels are instantiated: the rows of B and C in shared memory are padded to that)
     const int npt_t = big ? (npt <= 8 ? 8 : npt <= 16 ? 16 : 32) : (npt <= 4 ? 4 : npt <= 8 ? 8 : npt <= 16 ? 16 : npt <= 32 ? 32 : 64);
-    const size_t smem = ((size_t)M2_CHUNK * Ps + 2 * (size_t)M2_CHUNK * npt_t * parts + 2 * M2_CHUNK + (size_t)M2_CHUNK * parts * Ps) * sizeof(float);
+    int chunk = M2_CHUNK;
+    auto smem_of = [&](int ck) { return ((size_t)ck * Ps + 2 * (size_t)ck * npt_t * parts + 2 * ck + (size_t)ck * parts * Ps) * sizeof(float); };
+    while (chunk > 2 && smem_of(chunk) > 160 * 1024) chunk /= 2;
+    const size_t smem = smem_of(chunk);
     if (smem > 200 * 1024) return PLLM_ERR_LIMIT;
     const int chunks = (max_segment_tokens + M2_CONV_TOKENS - 1) / M2_CONV_TOKENS;
     PLLM_DISPATCH_DTYPE(dtype, {
@@ -273,7 +276,7 @@ PLLM_EXPORT int pllm_mamba2_mix(int dtype, const void* u, const void* conv_w, co
                        (const T*)u, u_width, inner, (const T*)conv_w, (const T*)conv_b, (const Segment*)segs, (const float*)state,
                        state_stride, conv_off, c_buf, channels, taps);
         ScanArgs a{threads, smem, dim3(n_segs, heads, slices), stream, u, u_width, 2 * inner + 2 * groups * N, inner, c_buf, channels, dt_bias,
-                   a_log, d_skip, segs, state, state_stride, conv_off, y_buf, heads, groups, P, Ps, N, taps, parts};
+                   a_log, d_skip, segs, state, state_stride, conv_off, y_buf, heads, groups, P, Ps, N, taps, parts, chunk};
         if (big) {
             if (npt_t == 8) launch_scan<T, 8, 1024>(a); else if (npt_t == 16) launch_scan<T, 16, 1024>(a); else launch_scan<T, 32, 1024>(a);
         } else if (npt_t == 4) launch_scan<T, 4, 256>(a);

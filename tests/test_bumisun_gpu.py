@@ -366,7 +366,7 @@ def run_mamba(dtype, cuts_by_request, heads, groups, P_, N, taps, norm_groups, s
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,groups,P_,N,taps,norm_groups", [(4, 1, 8, 16, 4, 1), (6, 2, 12, 10, 2, 3), (3, 1, 20, 7, 5, 1), (8, 4, 32, 64, 4, 2),
-                                                                 (2, 1, 64, 128, 4, 1), (6, 3, 8, 32, 1, 6), (1, 1, 128, 256, 3, 1)])
+                                                                 (2, 1, 64, 128, 4, 1), (6, 3, 8, 32, 1, 6), (1, 1, 128, 256, 3, 1), (2, 1, 64, 512, 4, 1)])
 def test_mamba2_whole_in_portions_and_token_by_token(dtype, heads, groups, P_, N, taps, norm_groups):
     L = 75
     cuts = [[L], [2] * 5 + [1, 1, 3, 17, 16, 20, 1, 1, 1, 1, 1, 1], [1] * L, [40, 35]]
