@@ -22,7 +22,8 @@
 enum : int { KID_MAMBA2 = 80 };
 
 #define M2_CONV_TOKENS 64      // tokens a CTA of the convolution
-#define M2_CHUNK 32            // tokens the scan fetches at a time, at most (fewer where shared memory is short)
+#define M2_CHUNK 32            // tokens the scan fetches at a time
+#define M2_CHUNK_SMALL 8       // ... where a wide state leaves little shared memory
 #define M2_MAX_TAPS 16
 
 struct Segment { int first, count, before, slot; };
@@ -67,11 +68,12 @@ __global__ void __launch_bounds__(128) mamba2_conv_kernel(const T* u, int u_widt
 // grid (segments, heads, slices of P): a CTA holds the columns [p0, p0 + P) of a head's state, P = Pf / slices (few
 // segments are cut into more slices, so that a prompt's recurrence runs on more SMs than the model has heads);
 // thread (part, e): value entry p0 + e, e = tid % P, state rows n = part, part + parts, ...
-template <typename T, int NPT, int MAXT>
+template <typename T, int NPT, int MAXT, int CK>
 __global__ void __launch_bounds__(MAXT) mamba2_scan_kernel(const T* u, int u_width, int dt_off, int conv_in_off, const float* c, int channels,
                                    const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
                                    const Segment* __restrict__ segs, float* state, long long state_stride, long long conv_off,
-                                   float* __restrict__ y, int heads, int groups, int Pf, int P, int N, int taps, int parts, int chunk) {
+                                   float* __restrict__ y, int heads, int groups, int Pf, int P, int N, int taps, int parts) {
+    constexpr int chunk = CK;                        // tokens fetched at a time
     extern __shared__ float smem[];
     const int NP = NPT * parts;                      // rows of B and C in shared memory: N, padded with zeros to what the threads hold
     float* x_s = smem;                              // [chunk][P]
@@ -220,17 +222,18 @@ __global__ void __launch_bounds__(256) mamba2_gate_norm_kernel(const float* y, c
 struct ScanArgs {
     int threads; size_t smem; dim3 grid; cudaStream_t stream; const void* u; int u_width, dt_off, conv_in_off; const float* c; int channels;
     const float *dt_bias, *a_log, *d_skip; const int* segs; float* state; long long state_stride, conv_off; float* y;
-    int heads, groups, Pf, P, N, taps, parts, chunk;
+    int heads, groups, Pf, P, N, taps, parts;
 };
 
-template <typename T, int NPT, int MAXT>
+template <typename T, int NPT, int MAXT, int CK>
 static void launch_scan(const ScanArgs& a) {
-    cudaFuncSetAttribute(mamba2_scan_kernel<T, NPT, MAXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)a.smem);
-    launch_chained(mamba2_scan_kernel<T, NPT, MAXT>, a.grid, dim3(a.threads), a.smem, a.stream, (const T*)a.u, a.u_width, a.dt_off,
+    cudaFuncSetAttribute(mamba2_scan_kernel<T, NPT, MAXT, CK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)a.smem);
+    launch_chained(mamba2_scan_kernel<T, NPT, MAXT, CK>, a.grid, dim3(a.threads), a.smem, a.stream, (const T*)a.u, a.u_width, a.dt_off,
                    a.conv_in_off, a.c, a.channels, a.dt_bias, a.a_log, a.d_skip, (const Segment*)a.segs, a.state, a.state_stride,
-                   a.conv_off, a.y, a.heads, a.groups, a.Pf, a.P, a.N, a.taps, a.parts, a.chunk);
+                   a.conv_off, a.y, a.heads, a.groups, a.Pf, a.P, a.N, a.taps, a.parts);
 }
 
+#define M2_SCAN(NPT_, MAXT_) do { if (chunk == M2_CHUNK) launch_scan<T, NPT_, MAXT_, M2_CHUNK>(a); else launch_scan<T, NPT_, MAXT_, M2_CHUNK_SMALL>(a); } while (0)
 // u: [tokens, 2 inner + 2 G N + heads] of the compute dtype; conv_w [channels, taps], conv_b [channels] of the same;
 // dt_bias, a_log, d_skip, gain float; state [slots, state_stride] float; c_buf [tokens, channels] and y_buf [tokens, inner]
 // float scratch; out [tokens, inner] of the compute dtype.  max_segment_tokens bounds a segment's tokens (the step's tokens).
@@ -267,7 +270,7 @@ PLLM_EXPORT int pllm_mamba2_mix(int dtype, const void* u, const void* conv_w, co
     const int npt_t = big ? (npt <= 8 ? 8 : npt <= 16 ? 16 : 32) : (npt <= 4 ? 4 : npt <= 8 ? 8 : npt <= 16 ? 16 : npt <= 32 ? 32 : 64);
     int chunk = M2_CHUNK;
     auto smem_of = [&](int ck) { return ((size_t)ck * Ps + 2 * (size_t)ck * npt_t * parts + 2 * ck + (size_t)ck * parts * Ps) * sizeof(float); };
-    while (chunk > 2 && smem_of(chunk) > 160 * 1024) chunk /= 2;
+    if (smem_of(chunk) > 160 * 1024) chunk = M2_CHUNK_SMALL;
     const size_t smem = smem_of(chunk);
     if (smem > 200 * 1024) return PLLM_ERR_LIMIT;
     const int chunks = (max_segment_tokens + M2_CONV_TOKENS - 1) / M2_CONV_TOKENS;
@@ -276,14 +279,14 @@ PLLM_EXPORT int pllm_mamba2_mix(int dtype, const void* u, const void* conv_w, co
                        (const T*)u, u_width, inner, (const T*)conv_w, (const T*)conv_b, (const Segment*)segs, (const float*)state,
                        state_stride, conv_off, c_buf, channels, taps);
         ScanArgs a{threads, smem, dim3(n_segs, heads, slices), stream, u, u_width, 2 * inner + 2 * groups * N, inner, c_buf, channels, dt_bias,
-                   a_log, d_skip, segs, state, state_stride, conv_off, y_buf, heads, groups, P, Ps, N, taps, parts, chunk};
+                   a_log, d_skip, segs, state, state_stride, conv_off, y_buf, heads, groups, P, Ps, N, taps, parts};
         if (big) {
-            if (npt_t == 8) launch_scan<T, 8, 1024>(a); else if (npt_t == 16) launch_scan<T, 16, 1024>(a); else launch_scan<T, 32, 1024>(a);
-        } else if (npt_t == 4) launch_scan<T, 4, 256>(a);
-        else if (npt_t == 8) launch_scan<T, 8, 256>(a);
-        else if (npt_t == 16) launch_scan<T, 16, 256>(a);
-        else if (npt_t == 32) launch_scan<T, 32, 256>(a);
-        else launch_scan<T, 64, 256>(a);
+            if (npt_t == 8) M2_SCAN(8, 1024); else if (npt_t == 16) M2_SCAN(16, 1024); else M2_SCAN(32, 1024);
+        } else if (npt_t == 4) M2_SCAN(4, 256);
+        else if (npt_t == 8) M2_SCAN(8, 256);
+        else if (npt_t == 16) M2_SCAN(16, 256);
+        else if (npt_t == 32) M2_SCAN(32, 256);
+        else M2_SCAN(64, 256);
         launch_chained(mamba2_gate_norm_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, (const float*)y_buf, (const T*)u, u_width, gain,
                        (T*)out, inner, norm_groups, eps);
     });
