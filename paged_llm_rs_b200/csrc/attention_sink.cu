@@ -324,7 +324,7 @@ __device__ __forceinline__ uint32_t sink_pack_bf16(float lo, float hi) {
 }
 
 template <int DK, int DV>
-__global__ void __launch_bounds__(128) attention_sink_mma_kernel(const bf16* q, const bf16* kv_pool, const int* __restrict__ block_tables,
+__global__ void __launch_bounds__(128, (DK + DV <= 192) ? 4 : 3) attention_sink_mma_kernel(const bf16* q, const bf16* kv_pool, const int* __restrict__ block_tables,
                                                                  const SinkWork* __restrict__ work, const int* __restrict__ n_work_ptr,
                                                                  bf16* __restrict__ out, float* __restrict__ part_o,
                                                                  float* __restrict__ part_ml, const float* __restrict__ sinks, int nh,
@@ -333,7 +333,7 @@ __global__ void __launch_bounds__(128) attention_sink_mma_kernel(const bf16* q, 
     constexpr int QS = DK + SMMA_PAD, KS = DK + SMMA_PAD, VS = DV + SMMA_PAD;      // row strides in elements
     extern __shared__ __align__(16) unsigned char sink_smem[];
     bf16* q_s = reinterpret_cast<bf16*>(sink_smem);            // [SMMA_ROWS][QS]
-    bf16* k_s = q_s + SMMA_ROWS * QS;                          // the tiles' place
+    bf16* k_s = q_s;                                           // the tiles' place: the queries' own, once they are in registers
     constexpr int TILE = SMMA_BK * (KS + VS);                  // a tile's keys [SMMA_BK][KS], then its values [SMMA_BK][VS]; two tiles
     pdl_launch_dependents();
     pdl_wait(KID_ATT_SINK);
@@ -365,6 +365,7 @@ __global__ void __launch_bounds__(128) attention_sink_mma_kernel(const bf16* q, 
     for (int kk = 0; kk < DK / 16; kk++)
         sink_ldmatrix_x4(qf[kk], sink_smem_u32(q_s + (row_base + (lane & 7) + ((lane >> 3) & 1) * 8) * QS + kk * 16 + (lane >> 4) * 8));
 
+    __syncthreads();                                 // every warp has its query fragments: the tiles may overwrite them
     // this thread's two rows: r0 = row_base + g and r0 + 8
     const int r0 = row_base + g, r1 = r0 + 8;
     const int pos0 = w.q_pos0 + (r0 < rows ? r0 / n_heads : 0), pos1 = w.q_pos0 + (r1 < rows ? r1 / n_heads : 0);
@@ -597,7 +598,8 @@ static int launch_sink_mma(const void* q, const void* kv_pool, const int* block_
     size_t tiles = 2 * ((size_t)SMMA_BK * (DK + SMMA_PAD) + (size_t)SMMA_BK * (DV + SMMA_PAD)) * sizeof(bf16);
     const size_t meet = (size_t)4 * 16 * (DV + 2) * sizeof(float);      // where the warps of a decoded token's item combine (the tiles' place)
     if (tiles < meet) tiles = meet;
-    const size_t smem = (size_t)SMMA_ROWS * (DK + SMMA_PAD) * sizeof(bf16) + tiles;
+    const size_t queries = (size_t)SMMA_ROWS * (DK + SMMA_PAD) * sizeof(bf16);     // (in registers before the first tile lands on them)
+    const size_t smem = tiles > queries ? tiles : queries;
     cudaFuncSetAttribute(attention_sink_mma_kernel<DK, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_chained(attention_sink_mma_kernel<DK, DV>, dim3(max_work, nkv * gparts), dim3(128), smem, stream, (const bf16*)q,
                    (const bf16*)kv_pool, block_tables, (const SinkWork*)work, n_work_ptr, (bf16*)out, part_o, part_ml, sinks, nh, nkv,
