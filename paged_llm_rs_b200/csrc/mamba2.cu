@@ -69,7 +69,7 @@ __global__ void __launch_bounds__(128) mamba2_conv_kernel(const T* u, int u_widt
 // segments are cut into more slices, so that a prompt's recurrence runs on more SMs than the model has heads);
 // thread (part, e): value entry p0 + e, e = tid % P, state rows n = part, part + parts, ...
 template <typename T, int NPT, int MAXT, int CK>
-__global__ void __launch_bounds__(MAXT) mamba2_scan_kernel(const T* u, int u_width, int dt_off, int conv_in_off, const float* c, int channels,
+__global__ void __launch_bounds__(MAXT, (MAXT == 256 && NPT <= 16) ? 3 : 1) mamba2_scan_kernel(const T* u, int u_width, int dt_off, int conv_in_off, const float* c, int channels,
                                    const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
                                    const Segment* __restrict__ segs, float* state, long long state_stride, long long conv_off,
                                    float* __restrict__ y, int heads, int groups, int Pf, int P, int N, int taps, int parts) {
@@ -254,6 +254,10 @@ PLLM_EXPORT int pllm_mamba2_mix(int dtype, const void* u, const void* conv_w, co
     // slices of at least 16 columns that divide P.
     int slices = 1;
     while (slices < 8 && (long long)n_segs * heads * slices < sm_count() && P % (2 * slices) == 0 && P / (2 * slices) >= 16) slices *= 2;
+    // ... and further while a thread would hold more than 16 state rows: three CTAs an SM instead of two keep more of the
+    // state's loads and stores in flight when many requests decode
+    while (slices < 8 && P % (2 * slices) == 0 && P / (2 * slices) >= 16 && (P / slices) <= 256 &&
+           (N + 256 / (P / slices) - 1) / (256 / (P / slices)) > 16) slices *= 2;
     const int Ps = P / slices;
     // threads of the scan: as many parts of Ps threads as fit 256 (1024 where a thread would hold more than 64 state rows;
     // a thread of 1024 holds 32 at most, for the registers to suffice)
@@ -270,7 +274,7 @@ PLLM_EXPORT int pllm_mamba2_mix(int dtype, const void* u, const void* conv_w, co
     const int npt_t = big ? (npt <= 8 ? 8 : npt <= 16 ? 16 : 32) : (npt <= 4 ? 4 : npt <= 8 ? 8 : npt <= 16 ? 16 : npt <= 32 ? 32 : 64);
     int chunk = M2_CHUNK;
     auto smem_of = [&](int ck) { return ((size_t)ck * Ps + 2 * (size_t)ck * npt_t * parts + 2 * ck + (size_t)ck * parts * Ps) * sizeof(float); };
-    if (smem_of(chunk) > 160 * 1024) chunk = M2_CHUNK_SMALL;
+    if (smem_of(chunk) > 160 * 1024 || max_segment_tokens <= M2_CHUNK_SMALL) chunk = M2_CHUNK_SMALL;   // (decoded tokens need no more)
     const size_t smem = smem_of(chunk);
     if (smem > 200 * 1024) return PLLM_ERR_LIMIT;
     const int chunks = (max_segment_tokens + M2_CONV_TOKENS - 1) / M2_CONV_TOKENS;
