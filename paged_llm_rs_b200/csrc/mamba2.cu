@@ -69,7 +69,7 @@ __global__ void __launch_bounds__(128) mamba2_conv_kernel(const T* u, int u_widt
 // segments are cut into more slices, so that a prompt's recurrence runs on more SMs than the model has heads);
 // thread (part, e): value entry p0 + e, e = tid % P, state rows n = part, part + parts, ...
 template <typename T, int NPT, int MAXT, int CK>
-__global__ void __launch_bounds__(MAXT, (MAXT == 256 && NPT <= 16) ? 3 : 1) mamba2_scan_kernel(const T* u, int u_width, int dt_off, int conv_in_off, const float* c, int channels,
+__global__ void __launch_bounds__(MAXT, (MAXT == 256 && NPT == 16) ? 3 : 1) mamba2_scan_kernel(const T* u, int u_width, int dt_off, int conv_in_off, const float* c, int channels,
                                    const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
                                    const Segment* __restrict__ segs, float* state, long long state_stride, long long conv_off,
                                    float* __restrict__ y, int heads, int groups, int Pf, int P, int N, int taps, int parts) {
