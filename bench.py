@@ -748,7 +748,8 @@ def hybrid_kernels(z, pk):
         if len(segs) > 1:
             sg[:, 0] = torch.arange(len(segs), dtype=torch.int32, device=dev)
         y = torch.empty(n, inner, dtype=bf, device=dev)
-        ms = timed(lambda: ops.mamba2_mix(u, cw, cb, hb, hb, hb, gain, sg, n, state, y, H, G, P_, N, taps, 1, 1e-6))
+        longest = max(c for _, c, _ in segs)
+        ms = timed(lambda: ops.mamba2_mix(u, cw, cb, hb, hb, hb, gain, sg, longest, state, y, H, G, P_, N, taps, 1, 1e-6))
         nbytes = u.numel() * 2 * 2 + n * ch * 4 * 2 + n * inner * 4 * 2 + y.numel() * 2 + len(segs) * floats * 4 * 2
         note(f"mamba2_mix_{case}", ms, nbytes, 6 * n * H * N * P_)
     return out

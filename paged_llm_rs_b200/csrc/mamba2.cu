@@ -68,8 +68,10 @@ __global__ void __launch_bounds__(128) mamba2_conv_kernel(const T* u, int u_widt
 // grid (segments, heads, slices of P): a CTA holds the columns [p0, p0 + P) of a head's state, P = Pf / slices (few
 // segments are cut into more slices, so that a prompt's recurrence runs on more SMs than the model has heads);
 // thread (part, e): value entry p0 + e, e = tid % P, state rows n = part, part + parts, ...
-template <typename T, int NPT, int MAXT, int CK>
-__global__ void __launch_bounds__(MAXT, (MAXT == 256 && NPT == 16) ? 3 : 1) mamba2_scan_kernel(const T* u, int u_width, int dt_off, int conv_in_off, const float* c, int channels,
+// MINB: CTAs an SM the registers are bounded for (three for decoded tokens where a thread holds sixteen state rows: more of
+// the state's loads and stores in flight; a prompt's long recurrence runs faster with the registers it likes)
+template <typename T, int NPT, int MAXT, int CK, int MINB>
+__global__ void __launch_bounds__(MAXT, MINB) mamba2_scan_kernel(const T* u, int u_width, int dt_off, int conv_in_off, const float* c, int channels,
                                    const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
                                    const Segment* __restrict__ segs, float* state, long long state_stride, long long conv_off,
                                    float* __restrict__ y, int heads, int groups, int Pf, int P, int N, int taps, int parts) {
@@ -225,15 +227,15 @@ struct ScanArgs {
     int heads, groups, Pf, P, N, taps, parts;
 };
 
-template <typename T, int NPT, int MAXT, int CK>
+template <typename T, int NPT, int MAXT, int CK, int MINB>
 static void launch_scan(const ScanArgs& a) {
-    cudaFuncSetAttribute(mamba2_scan_kernel<T, NPT, MAXT, CK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)a.smem);
-    launch_chained(mamba2_scan_kernel<T, NPT, MAXT, CK>, a.grid, dim3(a.threads), a.smem, a.stream, (const T*)a.u, a.u_width, a.dt_off,
+    cudaFuncSetAttribute(mamba2_scan_kernel<T, NPT, MAXT, CK, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)a.smem);
+    launch_chained(mamba2_scan_kernel<T, NPT, MAXT, CK, MINB>, a.grid, dim3(a.threads), a.smem, a.stream, (const T*)a.u, a.u_width, a.dt_off,
                    a.conv_in_off, a.c, a.channels, a.dt_bias, a.a_log, a.d_skip, (const Segment*)a.segs, a.state, a.state_stride,
                    a.conv_off, a.y, a.heads, a.groups, a.Pf, a.P, a.N, a.taps, a.parts);
 }
 
-#define M2_SCAN(NPT_, MAXT_) do { if (chunk == M2_CHUNK) launch_scan<T, NPT_, MAXT_, M2_CHUNK>(a); else launch_scan<T, NPT_, MAXT_, M2_CHUNK_SMALL>(a); } while (0)
+#define M2_SCAN(NPT_, MAXT_) do { if (chunk == M2_CHUNK) launch_scan<T, NPT_, MAXT_, M2_CHUNK, 1>(a); else launch_scan<T, NPT_, MAXT_, M2_CHUNK_SMALL, ((MAXT_) == 256 && (NPT_) == 16) ? 3 : 1>(a); } while (0)
 // u: [tokens, 2 inner + 2 G N + heads] of the compute dtype; conv_w [channels, taps], conv_b [channels] of the same;
 // dt_bias, a_log, d_skip, gain float; state [slots, state_stride] float; c_buf [tokens, channels] and y_buf [tokens, inner]
 // float scratch; out [tokens, inner] of the compute dtype.  max_segment_tokens bounds a segment's tokens (the step's tokens).
@@ -250,10 +252,11 @@ PLLM_EXPORT int pllm_mamba2_mix(int dtype, const void* u, const void* conv_w, co
     const int u_width = 2 * inner + 2 * groups * N + heads;
     const long long conv_off = (long long)heads * N * P;
     if (state_stride < conv_off + (long long)(taps - 1) * channels) return PLLM_ERR_SIZE;
-    // Slices of P: a step of few segments (a prompt's portion) is cut so that segments x heads x slices fills the SMs,
-    // slices of at least 16 columns that divide P.
+    // Slices of P: a step of few segments (a prompt's portion) is cut so that segments x heads x slices fills the SMs
+    // (one CTA an SM, or a few more: two CTAs of a long recurrence on one SM take nearly twice as long), slices of at
+    // least 16 columns that divide P.
     int slices = 1;
-    while (slices < 8 && (long long)n_segs * heads * slices < sm_count() && P % (2 * slices) == 0 && P / (2 * slices) >= 16) slices *= 2;
+    while (slices < 8 && (long long)n_segs * heads * slices * 2 <= sm_count() + sm_count() / 8 && P % (2 * slices) == 0 && P / (2 * slices) >= 16) slices *= 2;
     // ... and further while a thread would hold more than 16 state rows: three CTAs an SM instead of two keep more of the
     // state's loads and stores in flight when many requests decode
     while (slices < 8 && P % (2 * slices) == 0 && P / (2 * slices) >= 16 && (P / slices) <= 256 &&

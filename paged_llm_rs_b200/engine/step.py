@@ -217,6 +217,8 @@ class StepPacker:
                      groups=[dict(planned=p[2] is not None, parts=p[4], max_work=p[5], max_red=p[6], table_width=p[7])
                              for p in group_parts],
                      host_segments=segs,
+                     # the most tokens a request brings (a captured step: what its capacities allow)
+                     max_segment=((1 if caps.kinds == 1 else caps.tokens) if caps is not None else max((n for (_, n, _, _) in segs), default=0)),
                      # (a captured step of single tokens is cut for its capacity's worth of requests at the least)
                      plan_tokens=(caps.tokens if caps is not None and caps.kinds == 1 else n_seg) if (singles or caps) else 0)
         return host, layout, sizes
@@ -245,7 +247,8 @@ class StepPacker:
                                     slots=view(f"g{gi}.slots", T), plan=plan))
         state = StepState(n_tokens=T, tokens=view("tokens", T), positions=view("positions", T), groups=groups,
                           logit_rows=view("logit_rows", nw), n_wanted=nw,
-                          segments=view("segments").view(-1, 4), host_segments=list(sizes["host_segments"]))
+                          segments=view("segments").view(-1, 4), host_segments=list(sizes["host_segments"]),
+                          max_segment_tokens=int(sizes.get("max_segment", 0)))
         state.temperature = view("temperature", max(nw, 1)).view(torch.float32)
         state.uniform = view("uniform", max(nw, 1)).view(torch.float32)
         return state

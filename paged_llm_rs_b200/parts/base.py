@@ -229,6 +229,8 @@ class StepState:
     # what a layer hands to later layers of the same step (an early layer's values that later ones mix in, say), by name;
     # emptied when a step's forward pass begins
     carry: Dict[str, torch.Tensor] = field(default_factory=dict)
+    # the most tokens one request brings to the step (a captured step: its capacity allows); 0: not known
+    max_segment_tokens: int = 0
 
 
 # --- parts ------------------------------------------------------------------------

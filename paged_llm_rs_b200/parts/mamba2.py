@@ -59,7 +59,7 @@ class Mamba2Mixer(Mixer):
         st = self.rt.status
         u = ops.linear(x, self.w_in, status=st)
         y = torch.empty((x.shape[0], self.inner), dtype=x.dtype, device=x.device)
-        ops.mamba2_mix(u, self.conv_w, self.conv_b, self.dt_bias, self.a_log, self.d, self.gain, step.segments, step.n_tokens,
+        ops.mamba2_mix(u, self.conv_w, self.conv_b, self.dt_bias, self.a_log, self.d, self.gain, step.segments, step.max_segment_tokens or step.n_tokens,
                        cache, y, self.heads, self.groups, self.vdim, self.state, self.taps, self.norm_groups, self.eps)
         out = ops.linear(y, self.w_o, status=st)
         if self.rt.trace is not None:
